@@ -1,0 +1,316 @@
+#!/usr/bin/env python3
+"""Benchmark of the fused trellis decode-GEMV (the headline metric) on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N=1): benchmark configuration 2 restricted to the rate and row count the
+metric names -- K=4 bits/weight, one activation row -- over its four shapes
+(4096x4096, 5120x5120, 1152x4096, 4096x14336), seeded synthetic weights.  A "step" is
+one pass over every weight clone of every shape; each shape has enough clones to
+exceed L2 four times over, so weights always come from HBM.  `value` is packed weight
+bytes per second (the reference's own definition, README.md:224-226) with inputs
+resident on the device and every call captured in one CUDA graph.  `e2e` is the same
+metric through the public C-ABI call (strix_linear_plan_submit) with HOST activations:
+every call's input is copied from pinned host memory and its output copied back
+inside the timed region.
+
+With N>1 (launched under torchrun) every rank runs the same workload on its own GPU
+(replicas: the plain GEMV has no cross-GPU exchange) and the value is the sum.
+
+`--impl reference` times the CPU contract (this repository's C restatement of the
+reference's NumPy path, all host threads) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPES = [(4096, 4096), (5120, 5120), (1152, 4096), (4096, 14336)]
+BITS, ROWS = 4, 1
+METRIC = "K4 R1 decode-GEMV GB/s over packed weight bytes"
+WORKLOAD = "config2: K4 R1 fused decode-GEMV sweep over (4096,4096),(5120,5120),(1152,4096),(4096,14336)"
+
+
+def measured_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_baseline(seconds_budget=12.0):
+    """C restatement of the reference CPU contract, all host threads, on a sample: whole
+    K4 R1 layers of the smallest two shapes, repeated until the budget is spent."""
+    from oracle import c_oracle
+    from strix_trellis_b200 import synthetic
+    c_oracle.build()
+    layers = [synthetic.make_layer(i, n, BITS, seed=synthetic.BASE_SEED + k)
+              for k, (i, n) in enumerate([(1152, 4096), (4096, 4096)])]
+    xs = [synthetic.make_activations(ROWS, layer.inputs) for layer in layers]
+    for layer, x in zip(layers, xs):
+        c_oracle.linear(layer.trellis, layer.suh, layer.svh, None, BITS, 2, x)
+    done_bytes, calls, t0 = 0, 0, time.perf_counter()
+    while time.perf_counter() - t0 < seconds_budget:
+        for layer, x in zip(layers, xs):
+            c_oracle.linear(layer.trellis, layer.suh, layer.svh, None, BITS, 2, x)
+            done_bytes += layer.packed_bytes
+            calls += 1
+    dt = time.perf_counter() - t0
+    return {"value": done_bytes / dt / 1e9, "unit": "GB/s", "cores": c_oracle.threads(), "kind": "port",
+            "sample": f"{calls} whole K4 R1 layers of shapes (1152,4096),(4096,4096) in {dt:.1f} s"}, dt / max(calls, 1)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = []
+    base = None
+    for _ in range(args.warmup + args.steps):
+        base, _ = cpu_baseline(seconds_budget=max(2.0, 20.0 / max(args.steps + args.warmup, 1)))
+        per_step.append(base["value"])
+    vals = per_step[args.warmup:]
+    value = float(np.mean(vals))
+    base["value"] = value
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 weights, f32 accumulate",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "host": "CPU contract, all host threads"},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from strix_trellis_b200 import native as N, synthetic
+    from strix_trellis_b200.runtime import Context
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = Context(local)
+
+    # ---- weights: clones per shape so that each shape's rotation is >= 4x L2 ----------
+    rotation = 512 * 1024 * 1024
+    groups, total_bytes, launches = [], 0, 0
+    for k, (inputs, outputs) in enumerate(SHAPES):
+        layer = synthetic.make_layer(inputs, outputs, BITS, seed=synthetic.BASE_SEED + k)
+        clones = int(np.ceil(rotation / layer.packed_bytes))
+        ws = [ctx.prepare(layer) for _ in range(clones)]
+        x = torch.from_numpy(synthetic.make_activations(ROWS, inputs, seed=synthetic.BASE_SEED + 50 + k)).cuda()
+        y = torch.empty((ROWS, outputs), dtype=torch.float32, device="cuda")
+        groups.append(dict(layer=layer, weights=ws, x=x, y=y, hx=x.cpu().pin_memory(),
+                           hy=torch.empty((ROWS, outputs)).pin_memory()))
+        total_bytes += clones * layer.packed_bytes
+        launches += clones
+
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for g in groups:
+            g["plans"] = [w.plan(g["x"], g["y"], N.OP_GEMV, stream=stream) for w in g["weights"]]
+        for g in groups:  # correctness before timing: first clone against the CPU contract
+            g["plans"][0].submit()
+        stream.synchronize()
+    from oracle import c_oracle
+    for g in groups:
+        layer = g["layer"]
+        want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, None, BITS, 2, g["x"].cpu().numpy())
+        err = np.abs(g["y"].cpu().numpy() - want).max()
+        if not err <= 5e-4 * max(1.0, np.abs(want).max()):
+            raise SystemExit(f"output check failed before timing: maxabs {err}")
+
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for g in groups:
+                for p in g["plans"]:
+                    p.submit()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput: `value` -------------------------------------------
+    clocks = ClockSampler(local).__enter__()  # samples through the timed regions below
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        # keep the GPU under the same load until the sampler has a few readings
+        t_end = time.time() + 0.6
+        while time.time() < t_end:
+            graph.replay()
+        stream.synchronize()
+    # per-shape launch time (own event pairs, same graph nodes' plans, stream launches)
+    per_shape = {}
+    with torch.cuda.stream(stream):
+        for g in groups:
+            sub = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(sub, stream=stream):
+                for p in g["plans"]:
+                    p.submit()
+            sub.replay()
+            stream.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(3):
+                sub.replay()
+            b.record(stream)
+            stream.synchronize()
+            us = a.elapsed_time(b) * 1e3 / 3 / len(g["plans"])
+            layer = g["layer"]
+            per_shape[f"{layer.inputs}x{layer.outputs}"] = {
+                "us_per_launch": round(us, 3), "GBps": round(layer.packed_bytes / us / 1e3, 1)}
+            del sub
+    ms_t = torch.tensor([ms], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    ms = float(ms_t.item())
+    ms_per_step = ms / args.steps
+    value = world * total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: host activations in, host outputs out, per call ---------------------
+    e2e_steps = max(1, min(args.steps, 3))
+    h2d = sum(len(g["plans"]) * g["hx"].numel() * 4 for g in groups)
+    d2h = sum(len(g["plans"]) * g["hy"].numel() * 4 for g in groups)
+    with torch.cuda.stream(stream):
+        def e2e_pass():
+            for g in groups:
+                for p in g["plans"]:
+                    g["x"].copy_(g["hx"], non_blocking=True)
+                    p.submit()
+                    g["hy"].copy_(g["y"], non_blocking=True)
+        e2e_pass()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(e2e_steps):
+            e2e_pass()
+        b.record(stream)
+        barrier()
+        e2e_ms = a.elapsed_time(b) / e2e_steps
+    e2e_t = torch.tensor([e2e_ms], device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_value = world * total_bytes / (float(e2e_t.item()) * 1e-3) / 1e9
+
+    clocks.__exit__()
+    clock_summary = clocks.summary()
+    status = ctx.device_status()
+    if status:
+        raise SystemExit(f"device status word {status:#x}: a bounded wait gave up; numbers invalid")
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        avg_launch_us = ms_per_step * 1e3 / launches
+        achieved = total_bytes / launches / avg_launch_us / 1e3  # GB/s per launch, one GPU
+        traffic = None
+        tpath = ROOT / "profiles" / "gemv_k4_traffic.json"
+        if tpath.exists():
+            traffic = json.loads(tpath.read_text()).get("dram_bytes_per_packed_byte")
+        base, _ = cpu_baseline() if world == 1 else (None, None)
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 weights, f32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "bits": BITS, "rows": ROWS,
+                       "cold_weights": "each shape rotates over >=512 MiB of weight clones (>4x L2)",
+                       "launches_per_step": launches, "parallelism": f"replicas x{world}",
+                       "per_shape": per_shape},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "peak_kind": peak_kind,
+                         "traffic": None if traffic is None else round(traffic * total_bytes / launches),
+                         "kernel": "gemv_fused_kernel<4, mul1>",
+                         "algorithmic_bytes_per_launch": round(total_bytes / launches)},
+            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches * args.steps,
+            "clocks": clock_summary,
+        }
+        if base is not None:
+            line["cpu_baseline"] = base
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

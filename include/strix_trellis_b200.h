@@ -1,0 +1,68 @@
+/* strix_trellis_b200.h -- additions of the B200 runtime that the reference ABI has no
+ * name for.  None of them changes the behaviour of an entry point declared in
+ * strix_trellis.h.  Most are the stage probes that the reference keeps inside its GPU
+ * harness (tests/gpu_runtime.hip: isolated Q decode, input checkpoints,
+ * output_transform on a known core, docs/GPU_TESTS.md:97-109); here they are callable
+ * through the C ABI so that parity tests in any language can use them.
+ */
+#ifndef STRIX_TRELLIS_B200_H
+#define STRIX_TRELLIS_B200_H
+
+#include "strix_trellis.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Decode prepared weights to Q [I][N] binary16 (row-major, I rows) with the
+ * production decoder device function.  Stands in for the reference harness's
+ * isolated Q probe (tests/gpu_runtime.hip, docs/GPU_TESTS.md:97-100) and computes
+ * what python/strix_trellis/codec.py:165-173 (dequantize_rotated) computes.
+ * out_bytes >= I*N*2; device memory of the context's device. */
+strix_status strix_b200_dequantize(strix_context context, strix_weights weights, void *out_f16,
+                                   uint64_t out_bytes, const strix_stream *stream);
+
+/* Input checkpoints of the staged contract for x [rows][I] F32 (contiguous):
+ * scaled_f16 = RN16(RN32(x*suh)), hadamard_f32 = H128(scaled), core_f16 = RN16(hadamard)
+ * (python/strix_trellis/linear.py:111-124; reference kernel src/transforms.hpp:8-26).
+ * Any output pointer may be NULL.  Each non-NULL output holds rows*I elements. */
+strix_status strix_b200_input_stages(strix_context context, strix_weights weights, const float *x,
+                                     uint32_t rows, void *scaled_f16, float *hadamard_f32,
+                                     void *core_f16, const strix_stream *stream);
+
+/* Output stages on a caller-supplied core [splits][rows][N] F32: planes summed in
+ * ascending order from +0, H128, svh, bias, alpha, beta (linear.py:146-163; reference
+ * kernel src/transforms.hpp:28-52).  y is [rows][N] contiguous. */
+strix_status strix_b200_output_stages(strix_context context, strix_weights weights,
+                                      const float *core, uint32_t splits, uint32_t rows, float alpha,
+                                      float beta, float *y, const strix_stream *stream);
+
+/* Core product in the CPU contract's accumulation order (ascending input index, one
+ * fused multiply-add per term; bit-identical to linear.py:127-143 because products of
+ * two binary16 values are exact in binary32).  core_f16 [rows][I], core_out [rows][N],
+ * rows <= 64.  A parity instrument: slow, not a production path. */
+strix_status strix_b200_core_exact(strix_context context, strix_weights weights, const void *core_f16,
+                                   uint32_t rows, float *core_out, const strix_stream *stream);
+
+/* K partitions the fused GEMV uses for `rows` rows of these weights (fixes the
+ * association of the partial sums; counterpart of linear_split_count,
+ * src/backend.hip:22-45). */
+strix_status strix_b200_gemv_splits(strix_context context, strix_weights weights, uint32_t rows,
+                                    uint32_t *out_splits);
+
+/* Reads and clears the context's device status word.  Non-zero means that a bounded
+ * wait inside a kernel gave up (bit 0 weight ring full-wait, bit 1 empty-wait, bit 2
+ * drain at exit, bit 3 tensor pipeline); results of that launch are invalid.
+ * Synchronises the device.  No counterpart in the reference (its kernels never wait). */
+strix_status strix_b200_device_status(strix_context context, uint32_t *out_bits);
+
+/* Turns programmatic dependent launch of this library's kernels on (default) or off.
+ * With it, a kernel starts streaming its (immutable) weights while the previous
+ * kernel of the stream drains, and waits for that kernel before it reads activations
+ * or writes anything.  No counterpart in the reference. */
+strix_status strix_b200_set_programmatic_launch(strix_context context, uint32_t enabled);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STRIX_TRELLIS_B200_H */

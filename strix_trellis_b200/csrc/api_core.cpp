@@ -1,0 +1,200 @@
+// Host side of the C ABI: contexts, weight preparation, validation, gemv/gemm, frozen
+// plans, pre-routed grouped experts.  It mirrors the contract of the reference's
+// src/api.hip (status precedence, "validate everything before the first allocation or
+// enqueue", non-transactional grouped submission) against the CUDA runtime.
+#include "api_internal.h"
+
+namespace sapi {
+
+strix_status context_check(strix_context c) {
+    if (!c) return STRIX_ERROR_INVALID_ARGUMENT;
+    int device = -1;
+    const cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return cuda_status(e);
+    return device == c->device ? STRIX_SUCCESS : STRIX_ERROR_INVALID_ARGUMENT;
+}
+
+strix_status stream_check(strix_context c, const strix_stream* s, cudaStream_t& out) {
+    const strix_status st = header(s);
+    if (st != STRIX_SUCCESS) return st;
+    out = reinterpret_cast<cudaStream_t>(s->hip_stream);
+    if (!out) return STRIX_SUCCESS;
+    int device = -1;
+    unsigned int flags = 0;
+    if (cudaStreamGetDevice(out, &device) != cudaSuccess ||
+        cudaStreamGetFlags(out, &flags) != cudaSuccess || device != c->device) {
+        (void)cudaGetLastError();
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    }
+    return STRIX_SUCCESS;
+}
+
+// cuMemGetAddressRange through the runtime's driver entry point table: the library
+// does not link libcuda, so it loads on machines without a driver.
+typedef int (*AddressRangeFn)(unsigned long long*, size_t*, unsigned long long);
+static AddressRangeFn address_range_fn() {
+    static AddressRangeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            return (AddressRangeFn) nullptr;
+        }
+        return reinterpret_cast<AddressRangeFn>(p);
+    }();
+    return fn;
+}
+
+strix_status device_buffer(strix_context c, const void* p, uint64_t bytes, uint64_t align) {
+    if (!bytes) return STRIX_SUCCESS;
+    if (!p || !range_ok(p, bytes) || reinterpret_cast<uintptr_t>(p) % align)
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    }
+    if (attr.type != cudaMemoryTypeDevice || attr.device != c->device)
+        return STRIX_ERROR_INVALID_ARGUMENT;  // host, registered host and managed memory
+    AddressRangeFn range = address_range_fn();
+    if (!range) return STRIX_ERROR_INVALID_ARGUMENT;
+    unsigned long long base = 0;
+    size_t size = 0;
+    if (range(&base, &size, (unsigned long long)reinterpret_cast<uintptr_t>(p)) != 0)
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    const uintptr_t at = reinterpret_cast<uintptr_t>(p);
+    if (at < base || at - base > size || bytes > size - (at - base))
+        return STRIX_ERROR_INSUFFICIENT_BUFFER;
+    return STRIX_SUCCESS;
+}
+
+// ---- tensors ----------------------------------------------------------------------
+static strix_status tensor_check(const strix_tensor_desc& t, uint64_t width, uint32_t rank,
+                                 uint64_t rows, bool contiguous, uint64_t& stride, uint64_t& bytes) {
+    const strix_status s = header(&t);
+    if (s != STRIX_SUCCESS) return s;
+    if (enum_bits(t.dtype) != STRIX_DTYPE_F32 || t.rank != rank) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    if (rank == 1) {
+        if (t.shape[0] != width || t.shape[1] || t.strides[0] != 1 || t.strides[1])
+            return STRIX_ERROR_UNSUPPORTED_FORMAT;
+        stride = width;
+    } else {
+        if (t.shape[0] != rows || t.shape[1] != width || t.strides[1] != 1)
+            return STRIX_ERROR_UNSUPPORTED_FORMAT;
+        if (contiguous ? t.strides[0] != width : t.strides[0] < width)
+            return STRIX_ERROR_UNSUPPORTED_FORMAT;
+        stride = t.strides[0];
+    }
+    // accessed span: (rows-1)*stride + width elements
+    uint64_t elements = 0;
+    if (rows) {
+        if (!mul_ok(rows - 1, stride, elements) || elements > UINT64_MAX - width)
+            return STRIX_ERROR_INVALID_ARGUMENT;
+        elements += width;
+    }
+    if (!mul_ok(elements, sizeof(float), bytes) || !range_ok(t.data, bytes))
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    if (bytes > t.buffer_bytes) return STRIX_ERROR_INSUFFICIENT_BUFFER;
+    if (bytes && (!t.data || reinterpret_cast<uintptr_t>(t.data) % alignof(float)))
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    return STRIX_SUCCESS;
+}
+
+strix_status view_check(strix_context c, const strix_matmul_desc* d, bool contiguous, View& v) {
+    strix_status s = header(d);
+    if (s != STRIX_SUCCESS) return s;
+    if (!d->weights || d->weights->owner != c || !std::isfinite(d->alpha) || !std::isfinite(d->beta))
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    const st::DeviceWeights& w = d->weights->device;
+    const uint32_t rank = d->input.rank;
+    if (rank != 1 && rank != 2) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    const uint64_t rows = rank == 1 ? 1 : d->input.shape[0];
+    if (rows > INT_MAX) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    v.rows = static_cast<int>(rows);
+    s = tensor_check(d->input, (uint64_t)w.inputs, rank, rows, contiguous, v.x_stride, v.x_bytes);
+    if (s != STRIX_SUCCESS) return s;
+    s = tensor_check(d->output, (uint64_t)w.outputs, rank, rows, contiguous, v.y_stride, v.y_bytes);
+    if (s != STRIX_SUCCESS) return s;
+    const strix_weights_impl* wi = d->weights;
+    if (overlap(d->input.data, v.x_bytes, d->output.data, v.y_bytes) ||
+        overlap(d->input.data, v.x_bytes, wi->allocation, wi->allocation_bytes) ||
+        overlap(d->output.data, v.y_bytes, wi->allocation, wi->allocation_bytes))
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    return STRIX_SUCCESS;
+}
+
+st::LinearCall make_call(strix_context c, const strix_matmul_desc& d, const View& v) {
+    st::LinearCall call{};
+    call.w = d.weights->device;
+    call.x = static_cast<const float*>(d.input.data);
+    call.y = static_cast<float*>(d.output.data);
+    call.rows = v.rows;
+    call.x_stride = (long long)v.x_stride;
+    call.y_stride = (long long)v.y_stride;
+    call.alpha = d.alpha;
+    call.beta = d.beta;
+    call.status = c->status;
+    return call;
+}
+
+uint64_t linear_workspace(strix_context c, const st::DeviceWeights& w, int rows) {
+    if (rows <= 0) return 0;
+    if (rows <= 8) {
+        const st::GemvPlan p = st::plan_gemv(w, rows, c->sm_count);
+        return p.counter_bytes + p.partial_bytes;
+    }
+    return st::plan_gemm(w, rows, c->sm_count).workspace_bytes;
+}
+
+cudaError_t enqueue_linear(strix_context c, const st::LinearCall& call, void* workspace,
+                           bool zero_counters, cudaStream_t stream) {
+    if (call.rows <= 8) {
+        const st::GemvPlan p = st::plan_gemv(call.w, call.rows, c->sm_count);
+        if (p.counter_bytes && zero_counters) {
+            const cudaError_t e = cudaMemsetAsync(workspace, 0, p.counter_bytes, stream);
+            if (e != cudaSuccess) return e;
+        }
+        return st::launch_gemv(call, p, workspace, c->programmatic_launch, stream);
+    }
+    return st::launch_gemm(call, st::plan_gemm(call.w, call.rows, c->sm_count), workspace, stream);
+}
+
+// workspace declared by the caller: size, alignment, aliasing, then device provenance
+strix_status storage_check(strix_context c, const strix_matmul_desc& d, const View& v,
+                                  uint64_t needed, void* workspace, uint64_t bytes) {
+    if (bytes < needed) return STRIX_ERROR_INSUFFICIENT_BUFFER;
+    if (!range_ok(workspace, bytes) ||
+        (bytes && (!workspace || reinterpret_cast<uintptr_t>(workspace) % kAlign)))
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    const strix_weights_impl* wi = d.weights;
+    if (overlap(workspace, bytes, d.input.data, v.x_bytes) ||
+        overlap(workspace, bytes, d.output.data, v.y_bytes) ||
+        overlap(workspace, bytes, wi->allocation, wi->allocation_bytes))
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    if (!v.rows) return STRIX_SUCCESS;  // empty call: no device inspection at all
+    strix_status s = device_buffer(c, d.input.data, v.x_bytes, alignof(float));
+    if (s != STRIX_SUCCESS) return s;
+    s = device_buffer(c, d.output.data, v.y_bytes, alignof(float));
+    if (s != STRIX_SUCCESS) return s;
+    return device_buffer(c, workspace, bytes, kAlign);
+}
+
+strix_status submit(strix_context c, const strix_matmul_desc* d, const strix_stream* stream,
+                           bool gemv) {
+    strix_status s = context_check(c);
+    if (s != STRIX_SUCCESS) return s;
+    cudaStream_t cs{};
+    s = stream_check(c, stream, cs);
+    if (s != STRIX_SUCCESS) return s;
+    View v{};
+    s = view_check(c, d, true, v);
+    if (s != STRIX_SUCCESS) return s;
+    if ((gemv && v.rows > 8) || (!gemv && d->input.rank != 2)) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    const uint64_t needed = linear_workspace(c, d->weights->device, v.rows);
+    s = storage_check(c, *d, v, needed, d->workspace, d->workspace_bytes);
+    if (s != STRIX_SUCCESS || !v.rows) return s;
+    return cuda_status(enqueue_linear(c, make_call(c, *d, v), d->workspace, true, cs));
+}
+
+}  // namespace sapi

@@ -1,0 +1,101 @@
+// Entry points declared in strix_trellis_b200.h: stage probes and runtime switches.
+#include "api_internal.h"
+
+using namespace sapi;
+
+namespace {
+strix_status begin(strix_context c, strix_weights w, const strix_stream* stream, cudaStream_t& cs) {
+    strix_status s = context_check(c);
+    if (s != STRIX_SUCCESS) return s;
+    if (!w || w->owner != c) return STRIX_ERROR_INVALID_ARGUMENT;
+    return stream_check(c, stream, cs);
+}
+}  // namespace
+
+extern "C" {
+
+strix_status strix_b200_dequantize(strix_context c, strix_weights w, void* out_f16, uint64_t out_bytes,
+                                   const strix_stream* stream) {
+    cudaStream_t cs{};
+    strix_status s = begin(c, w, stream, cs);
+    if (s != STRIX_SUCCESS) return s;
+    const uint64_t need = (uint64_t)w->device.inputs * w->device.outputs * 2;
+    if (out_bytes < need) return STRIX_ERROR_INSUFFICIENT_BUFFER;
+    s = device_buffer(c, out_f16, need, 2);
+    if (s != STRIX_SUCCESS) return s;
+    return cuda_status(st::launch_dequantize(w->device, static_cast<uint16_t*>(out_f16), cs));
+}
+
+strix_status strix_b200_input_stages(strix_context c, strix_weights w, const float* x, uint32_t rows,
+                                     void* scaled_f16, float* hadamard_f32, void* core_f16,
+                                     const strix_stream* stream) {
+    cudaStream_t cs{};
+    strix_status s = begin(c, w, stream, cs);
+    if (s != STRIX_SUCCESS) return s;
+    if (!rows) return STRIX_SUCCESS;
+    const uint64_t n = (uint64_t)rows * w->device.inputs;
+    s = device_buffer(c, x, n * 4, 4);
+    if (s == STRIX_SUCCESS && scaled_f16) s = device_buffer(c, scaled_f16, n * 2, 2);
+    if (s == STRIX_SUCCESS && hadamard_f32) s = device_buffer(c, hadamard_f32, n * 4, 4);
+    if (s == STRIX_SUCCESS && core_f16) s = device_buffer(c, core_f16, n * 2, 2);
+    if (s != STRIX_SUCCESS) return s;
+    return cuda_status(st::launch_input_stages(w->device, x, w->device.inputs, (int)rows,
+                                               static_cast<uint16_t*>(scaled_f16), hadamard_f32,
+                                               static_cast<uint16_t*>(core_f16), cs));
+}
+
+strix_status strix_b200_output_stages(strix_context c, strix_weights w, const float* core,
+                                      uint32_t splits, uint32_t rows, float alpha, float beta, float* y,
+                                      const strix_stream* stream) {
+    cudaStream_t cs{};
+    strix_status s = begin(c, w, stream, cs);
+    if (s != STRIX_SUCCESS) return s;
+    if (!std::isfinite(alpha) || !std::isfinite(beta) || !splits) return STRIX_ERROR_INVALID_ARGUMENT;
+    if (!rows) return STRIX_SUCCESS;
+    const uint64_t n = (uint64_t)rows * w->device.outputs;
+    s = device_buffer(c, core, n * 4 * splits, 4);
+    if (s == STRIX_SUCCESS) s = device_buffer(c, y, n * 4, 4);
+    if (s != STRIX_SUCCESS) return s;
+    return cuda_status(st::launch_output_stages(w->device, core, (int)splits, (int)rows, y,
+                                                w->device.outputs, alpha, beta, cs));
+}
+
+strix_status strix_b200_core_exact(strix_context c, strix_weights w, const void* core_f16, uint32_t rows,
+                                   float* core_out, const strix_stream* stream) {
+    cudaStream_t cs{};
+    strix_status s = begin(c, w, stream, cs);
+    if (s != STRIX_SUCCESS) return s;
+    if (rows < 1 || rows > 64) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    s = device_buffer(c, core_f16, (uint64_t)rows * w->device.inputs * 2, 2);
+    if (s == STRIX_SUCCESS) s = device_buffer(c, core_out, (uint64_t)rows * w->device.outputs * 4, 4);
+    if (s != STRIX_SUCCESS) return s;
+    return cuda_status(st::launch_core_exact(w->device, static_cast<const uint16_t*>(core_f16), (int)rows,
+                                             core_out, cs));
+}
+
+strix_status strix_b200_gemv_splits(strix_context c, strix_weights w, uint32_t rows, uint32_t* out) {
+    if (!out) return STRIX_ERROR_INVALID_ARGUMENT;
+    *out = 0;
+    if (!c || !w || w->owner != c || rows < 1 || rows > 8) return STRIX_ERROR_INVALID_ARGUMENT;
+    *out = (uint32_t)st::plan_gemv(w->device, (int)rows, c->sm_count).splits;
+    return STRIX_SUCCESS;
+}
+
+strix_status strix_b200_device_status(strix_context c, uint32_t* out_bits) {
+    if (!out_bits) return STRIX_ERROR_INVALID_ARGUMENT;
+    *out_bits = 0;
+    const strix_status s = context_check(c);
+    if (s != STRIX_SUCCESS) return s;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(out_bits, c->status, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemset(c->status, 0, sizeof(uint32_t));
+    return cuda_status(e);
+}
+
+strix_status strix_b200_set_programmatic_launch(strix_context c, uint32_t enabled) {
+    if (!c) return STRIX_ERROR_INVALID_ARGUMENT;
+    c->programmatic_launch = enabled != 0;
+    return STRIX_SUCCESS;
+}
+
+}  // extern "C"

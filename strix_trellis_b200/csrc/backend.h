@@ -1,0 +1,89 @@
+// Interface between the host API layer (api.cpp) and the CUDA kernels (*.cu).
+// Everything here is plain data and plain functions: no allocation, transfer or
+// synchronisation happens behind a launch_* call.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace st {
+
+// Prepared weights on the device.  `packed` holds the tiles regrouped per 128 output
+// columns: [N/128][I/16][8 column tiles][8*bits uint32 words]; a column block is one
+// contiguous stream of I*16*bits bytes.
+struct DeviceWeights {
+    const uint32_t* packed;
+    const uint16_t* suh;  // binary16 bits [inputs]
+    const uint16_t* svh;  // binary16 bits [outputs]
+    const float* bias;    // [outputs] or nullptr
+    int inputs;
+    int outputs;
+    int bits;
+    int codebook;
+};
+
+// Row views: element (r, c) of x is x[r * x_stride + c]; likewise y.
+struct LinearCall {
+    DeviceWeights w;
+    const float* x;
+    float* y;
+    int rows;
+    long long x_stride;
+    long long y_stride;
+    float alpha;
+    float beta;
+    unsigned int* status;  // device word that collects bounded-wait failures (may be null)
+};
+
+constexpr size_t kAlign = 256;
+inline size_t align_up(size_t v, size_t a = kAlign) { return (v + a - 1) / a * a; }
+
+// ---- one-time regrouping of the transport tile order -----------------------------
+// src: [I/16][N/16][8*bits] words (transport order), dst: the prepared order above.
+cudaError_t launch_regroup(const uint32_t* src, uint32_t* dst, int inputs, int outputs, int bits,
+                           cudaStream_t stream);
+
+// ---- stage probes (parity instruments, same device functions as production) -------
+cudaError_t launch_dequantize(const DeviceWeights& w, uint16_t* q_out /*[I][N] f16 bits*/,
+                              cudaStream_t stream);
+cudaError_t launch_input_stages(const DeviceWeights& w, const float* x, long long x_stride, int rows,
+                                uint16_t* scaled16, float* hadamard32, uint16_t* core16,
+                                cudaStream_t stream);
+cudaError_t launch_output_stages(const DeviceWeights& w, const float* core /*[splits][rows][N]*/,
+                                 int splits, int rows, float* y, long long y_stride, float alpha,
+                                 float beta, cudaStream_t stream);
+// Sequential ascending-i fused multiply-add core, one thread per output: reproduces
+// the CPU contract's accumulation order bit for bit (products of two binary16 values
+// are exact in float32, so fma(a,q,acc) == RN32(acc + RN32(a*q))).
+cudaError_t launch_core_exact(const DeviceWeights& w, const uint16_t* core16 /*[rows][I]*/, int rows,
+                              float* core_out /*[rows][N]*/, cudaStream_t stream);
+
+// ---- decode GEMV, rows 1..8, everything fused ---------------------------------------
+struct GemvPlan {
+    int grid;            // persistent CTAs (one per SM, fewer for tiny layers)
+    int splits;          // typical number of CTAs that share one column block
+    int stages;          // shared-memory ring depth
+    int act_blocks;      // H128 blocks of core input staged at a time
+    size_t smem_bytes;
+    size_t counter_bytes;   // arrival counters [N/128] at the start of the workspace
+    size_t partial_bytes;   // float [grid][2][rows][128] after the counters
+};
+GemvPlan plan_gemv(const DeviceWeights& w, int rows, int sm_count);
+// `workspace` must be 256-byte aligned and hold counter_bytes + partial_bytes.  The
+// counters must be zero when the kernel starts; it leaves them zero.
+cudaError_t launch_gemv(const LinearCall& call, const GemvPlan& plan, void* workspace,
+                        bool programmatic_launch, cudaStream_t stream);
+
+// ---- prefill GEMM (rows > 8): input stage kernel + tcgen05 core with fused epilogue ---
+struct GemmPlan {
+    size_t act_bytes;       // binary16 [rows_padded][I] core input
+    size_t workspace_bytes;
+    int tile_m, tile_n;
+    int sm_count;
+    bool tensor_core;       // tcgen05 prefill kernel selected (else 8-row GEMV chunks)
+};
+GemmPlan plan_gemm(const DeviceWeights& w, int rows, int sm_count);
+cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* workspace,
+                        cudaStream_t stream);
+
+}  // namespace st

@@ -1,0 +1,383 @@
+// Fused decode GEMV for 1..8 activation rows: input stages (suh scale, RN16, H128,
+// RN16), trellis decode, tensor-core dot, split-K fold, output H128, svh, bias and
+// alpha/beta in ONE launch.  It stands in for the reference's input_transform +
+// gemv_lds_kernel + output_transform sequence (src/backend.hip:102-151,
+// src/gemv_lds.hip:93-167, src/transforms.hpp:8-52) and for its fused R1 variants
+// (src/gemv_fused.hip:17-129, src/gemv_fused_both.hip:10-93).
+//
+// Work split ("stream-K"): the weights are one byte stream of units, a unit being the
+// 64 tiles of (one 128-column block) x (one H128 block of K), ordered column block
+// major -- exactly the prepared layout.  The grid is one persistent CTA per SM and CTA
+// c owns the contiguous unit range [c*U/G, (c+1)*U/G): every SM streams the same number
+// of bytes (+-1 unit) through a shared-memory ring filled by 1-D bulk copies.  Sixteen
+// decode warps: warp (t, g) owns column tile t of the units of parity g, so the two warp
+// groups leapfrog through the ring.  A decoded tile is the A operand of mma.sync.m16n8k16 (m = output column), the
+// activation rows are the B operand (n = row), so 1..8 rows cost the same tensor work.
+//
+// Fold: a column block that lies inside one CTA's range is finished by that CTA.  A
+// column block shared by several CTAs gets one partial plane per CTA in global scratch
+// and one arrival atomic per CTA; the last CTA to arrive folds the planes in ascending
+// K order from +0 (never in arrival order, never spinning -- the reference's scheme,
+// src/gemv_fused.hip:81-127) and applies the output stages.  All of that is done by a
+// separate epilogue warp: decode warps only drop their accumulators into a double-buffered
+// shared-memory area and move on, so no decode warp ever waits on global-memory latency.
+#include <cstdlib>
+
+#include "backend.h"
+#include "hadamard.cuh"
+#include "sync_primitives.cuh"
+#include "trellis_decode.cuh"
+
+namespace st {
+
+namespace {
+constexpr int kGroups = 2;                       // k-tile parities per column tile
+constexpr int kConsumers = 8 * kGroups;          // decode warps
+constexpr int kThreads = (kConsumers + 2) * 32;  // + producer warp + epilogue warp
+constexpr int kDumpThreads = (kConsumers + 1) * 32;  // decode warps + epilogue warp
+constexpr int kActBytes = 32 * 1024;             // staged core input per CTA
+
+struct GemvArgs {
+    LinearCall call;
+    int stages;
+    int act_blocks;            // H128 blocks of core input staged at a time
+    unsigned int* counters;    // [N/128], zero on entry, zero on exit
+    float* partials;           // [grid][2][rows][128]
+#ifdef ST_TIMELINE
+    unsigned long long* timeline;
+#endif
+};
+
+__host__ __device__ inline int stage_bytes(int bits) { return 2048 * bits; }
+
+struct Range { long long begin, end; };
+__host__ __device__ inline Range cta_range(long long units, int grid, int c) {
+    return Range{units * c / grid, units * (c + 1) / grid};
+}
+// CTAs whose ranges intersect the units [lo, hi) of one column block.
+__host__ __device__ inline void contributors(long long units, int grid, long long lo, long long hi,
+                                             int& first, int& last) {
+    int c = (int)(lo * grid / units);
+    if (c >= grid) c = grid - 1;
+    while (c > 0 && cta_range(units, grid, c).begin > lo) --c;
+    while (cta_range(units, grid, c).end <= lo) ++c;
+    first = c;
+    c = (int)((hi - 1) * grid / units);
+    if (c >= grid) c = grid - 1;
+    while (c + 1 < grid && cta_range(units, grid, c + 1).begin < hi) ++c;
+    while (cta_range(units, grid, c).begin >= hi) --c;
+    last = c;
+}
+}  // namespace
+
+template <int K, int CB>
+__global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs args) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const LinearCall& c = args.call;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rows = c.rows;
+    const int hblocks = c.w.inputs / 128, nblocks = c.w.outputs / 128;
+    const long long units = (long long)hblocks * nblocks;
+    const int grid = (int)gridDim.x, cta = (int)blockIdx.x;
+    const Range mine = cta_range(units, grid, cta);
+    const int my_units = (int)(mine.end - mine.begin);
+    const int stages = args.stages;
+    constexpr int kStage = 2048 * K;
+
+    // shared memory: [2 x fold 8 KB][barriers 512 B][ring][core input]
+    float* fold_base = reinterpret_cast<float*>(smem);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 16384);
+    unsigned char* ring = smem + 16384 + 512;
+    uint2* act = reinterpret_cast<uint2*>(ring + (size_t)stages * kStage);
+
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + stages);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < stages; ++i) {
+            mbar_init(full0 + 8 * i, 1);
+            mbar_init(empty0 + 8 * i, 8);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+#ifdef ST_TIMELINE
+    auto stamp = [&](int slot) {
+        if (args.timeline && (threadIdx.x == 0 || (slot == 6 && threadIdx.x == 32 * kConsumers))) {
+            unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+            args.timeline[(size_t)blockIdx.x * 8 + slot] = t;
+            if (slot == 3) args.timeline[(size_t)blockIdx.x * 8 + 7] = (unsigned long long)clock64();
+            if (slot == 4) args.timeline[(size_t)blockIdx.x * 8 + 7] = (unsigned long long)clock64() - args.timeline[(size_t)blockIdx.x * 8 + 7];
+        }
+    };
+#else
+    auto stamp = [](int) {};
+#endif
+    stamp(0);
+    pdl_launch_dependents();
+
+    if (warp == kConsumers) {
+        // ---- producer: weights are immutable, so this needs no wait on the prior grid ----
+        if (lane == 0) {
+            const unsigned char* stream =
+                reinterpret_cast<const unsigned char*>(c.w.packed) + (size_t)mine.begin * kStage;
+            int issued = 0;
+            for (int i = 0; i < my_units; ++i) {
+                const int st = i % stages;
+                if (i >= stages &&
+                    !mbar_wait(empty0 + 8 * st, ((i / stages) - 1) & 1, c.status, kTimeoutRingEmpty))
+                    break;
+                mbar_expect_tx(full0 + 8 * st, kStage);
+                bulk_load(smem_u32(ring + (size_t)st * kStage), stream + (size_t)i * kStage, kStage,
+                          full0 + 8 * st);
+                issued = i + 1;
+            }
+            stamp(6);
+            // Never leave the CTA with a copy still landing in its shared memory.
+            for (int i = (issued > stages ? issued - stages : 0); i < issued; ++i)
+                mbar_wait(full0 + 8 * (i % stages), (i / stages) & 1, c.status, kTimeoutDrain);
+        }
+        return;
+    }
+
+    // Segment walk shared by decode and epilogue warps: the CTA's unit range is cut at
+    // column-block ends (where a contribution is flushed) and at the staging capacity.
+    auto segment = [&](int done, int& nb, int& hb0, int& len) {
+        const long long u = mine.begin + done;
+        nb = (int)(u / hblocks);
+        hb0 = (int)(u % hblocks);
+        len = my_units - done;
+        if (len > hblocks - hb0) len = hblocks - hb0;
+        if (len > args.act_blocks) len = args.act_blocks;
+    };
+
+    if (warp == kConsumers + 1) {
+        // ---- epilogue warp: turns dumped accumulators into partial planes or outputs ------
+        pdl_wait_prior_grid();  // y, scratch and counters may belong to the prior grid
+        int done = 0, flush = 0;
+        while (done < my_units) {
+            int nb, hb0, len;
+            segment(done, nb, hb0, len);
+            done += len;
+            if (!((hb0 + len == hblocks) || (done == my_units))) continue;
+            const int buf = flush & 1;
+            named_barrier(2 + buf, kDumpThreads);  // all decode warps have dumped into `buf`
+            const float* f0 = fold_base + buf * 2048;
+            const long long blk_lo = (long long)nb * hblocks, blk_hi = blk_lo + hblocks;
+            const bool whole = mine.begin <= blk_lo && mine.end >= blk_hi;
+            int first = cta, last = cta;
+            bool finish = whole;
+            if (!whole) {
+                contributors(units, grid, blk_lo, blk_hi, first, last);
+                float* plane = args.partials + ((size_t)cta * 2 + (mine.begin > blk_lo ? 0 : 1)) * rows * 128;
+                for (int e = lane; e < rows * 128; e += 32)  // k-groups in ascending order
+                    plane[e] = __fadd_rn(f0[e], f0[1024 + e]);
+                __threadfence();
+                __syncwarp();
+                unsigned int seen = 0;
+                if (lane == 0) seen = atomicAdd(&args.counters[nb], 1u);
+                seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
+                finish = (seen == (unsigned int)(last - first));
+                if (finish) {
+                    if (lane == 0) args.counters[nb] = 0;
+                    __threadfence();
+                }
+            }
+            if (finish) {
+                for (int r = 0; r < rows; ++r) {
+                    float v[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (whole) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            v[j] = __fadd_rn(0.f, __fadd_rn(f0[r * 128 + lane + 32 * j], f0[1024 + r * 128 + lane + 32 * j]));
+                    } else {
+                        for (int p = first; p <= last; ++p) {  // ascending K order
+                            const int slot = cta_range(units, grid, p).begin > blk_lo ? 0 : 1;
+                            const float* plane = args.partials + ((size_t)p * 2 + slot) * rows * 128 + r * 128;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) v[j] = __fadd_rn(v[j], __ldcg(plane + lane + 32 * j));
+                        }
+                    }
+                    hadamard128_warp(v, lane);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int cidx = nb * 128 + lane + 32 * j;
+                        float* out = c.y + (long long)r * c.y_stride + cidx;
+                        *out = finish_output(v[j], c.w.svh[cidx], c.w.bias, cidx, c.alpha, c.beta, out);
+                    }
+                }
+            }
+            // hand the buffer back (decode warps wait on this before its next reuse)
+            asm volatile("bar.arrive %0, %1;" ::"r"(4 + buf), "r"(kDumpThreads) : "memory");
+            ++flush;
+        }
+        stamp(5);
+        return;
+    }
+
+    // ---- decode warps -------------------------------------------------------------------
+    pdl_wait_prior_grid();  // x may belong to the prior grid
+    stamp(2);
+    const int ctile = warp & 7, kgroup = warp >> 3;
+    const LaneGeom<K> geom(lane);
+    // Row fed by this lane as the B operand.  Rows >= `rows` only reach accumulator
+    // columns that are never read, so those lanes may load any valid row.
+    const int brow = (lane >> 2) < rows ? (lane >> 2) : rows - 1;
+    const uint2* act_lane = act + brow * 32 + (lane & 3);
+    __half* act_h = reinterpret_cast<__half*>(act);
+    const int col = ctile * 16 + (lane >> 2), r0 = 2 * (lane & 3);
+
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    bool ok = true;
+    int done = 0, flush = 0;
+    while (done < my_units) {
+        int nb, hb0, len;
+        segment(done, nb, hb0, len);
+
+        // input stages for H128 blocks [hb0, hb0+len), written in B-fragment order:
+        // act[((blk*rows + r)*8 + kt)*4 + q] = {half2(k0,k0+1), half2(k0+8,k0+9)}, k0 = 2q
+        named_barrier(1, kConsumers * 32);  // previous chunk's readers are done
+        for (int item = warp; item < rows * len; item += kConsumers) {
+            const int r = item / len, blk = item % len;
+            const float* xr = c.x + (long long)r * c.x_stride + (size_t)(hb0 + blk) * 128;
+            const uint16_t* su = c.w.suh + (size_t)(hb0 + blk) * 128;
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = __half2float(scale_input(xr[lane + 32 * j], su[lane + 32 * j]));
+            hadamard128_warp(v, lane);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int e = lane + 32 * j, kt = e >> 4, kk = e & 15;
+                const int q = (kk & 7) >> 1, hi = kk >> 3, lo = kk & 1;
+                act_h[((((size_t)blk * rows + r) * 8 + kt) * 4 + q) * 4 + hi * 2 + lo] = __float2half_rn(v[j]);
+            }
+        }
+        named_barrier(1, kConsumers * 32);
+        if (done == 0) stamp(3);
+
+        // this warp group takes the units of its parity (ring slots alternate with them)
+        for (int b = ((done & 1) == kgroup) ? 0 : 1; b < len && ok; b += 2) {
+            const int i = done + b, st = i % stages;
+            ok = mbar_wait(full0 + 8 * st, (i / stages) & 1, c.status, kTimeoutRingFull);
+            if (!ok) break;
+            const uint32_t* tiles =
+                reinterpret_cast<const uint32_t*>(ring + (size_t)st * kStage) + ctile * (8 * K);
+            const uint2* bsrc = act_lane + (size_t)b * rows * 32;
+#pragma unroll
+            for (int kt = 0; kt < 8; kt += 2) {  // two independent tiles in flight
+                uint32_t fa[4], fb[4];
+                decode_tile_frag<K, CB>(tiles + kt * 8 * (8 * K), geom, fa);
+                decode_tile_frag<K, CB>(tiles + (kt + 1) * 8 * (8 * K), geom, fb);
+                const uint2 ba = bsrc[kt * 4], bb = bsrc[(kt + 1) * 4];
+                mma_16816(acc[0], fa, ba.x, ba.y);
+                mma_16816(acc[1], fb, bb.x, bb.y);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * st);
+        }
+        done += len;
+        if (done == my_units) stamp(4);
+        if (!((hb0 + len == hblocks) || (done == my_units))) continue;
+
+        // ---- drop this CTA's contribution to column block nb and move on --------------------
+        // c0,c1: column ctile*16 + lane/4, rows 2(lane%4), +1; c2,c3: column + 8
+        const int buf = flush & 1;
+        if (flush >= 2) named_barrier(4 + buf, kDumpThreads);  // epilogue is done with `buf`
+        {
+            float* g = fold_base + buf * 2048 + kgroup * 1024;
+            const float v00 = acc[0][0] + acc[1][0], v01 = acc[0][1] + acc[1][1];
+            const float v10 = acc[0][2] + acc[1][2], v11 = acc[0][3] + acc[1][3];
+            if (r0 < rows) { g[r0 * 128 + col] = v00; g[r0 * 128 + col + 8] = v10; }
+            if (r0 + 1 < rows) { g[(r0 + 1) * 128 + col] = v01; g[(r0 + 1) * 128 + col + 8] = v11; }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[0][j] = acc[1][j] = 0.f;
+        }
+        asm volatile("bar.arrive %0, %1;" ::"r"(2 + buf), "r"(kDumpThreads) : "memory");
+        ++flush;
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------
+static int gemv_grid(const DeviceWeights& w, int sm_count) {
+    const long long units = (long long)(w.inputs / 128) * (w.outputs / 128);
+    return (int)(units < sm_count ? units : sm_count);
+}
+
+GemvPlan plan_gemv(const DeviceWeights& w, int rows, int sm_count) {
+    GemvPlan plan{};
+    const int hblocks = w.inputs / 128, nblocks = w.outputs / 128;
+    const int grid = gemv_grid(w, sm_count);
+    const long long units = (long long)hblocks * nblocks;
+    const int per_cta = (int)((units + grid - 1) / grid);
+    int act_blocks = kActBytes / (256 * rows);
+    if (act_blocks > hblocks) act_blocks = hblocks;
+    int stages = (96 * 1024) / stage_bytes(w.bits);
+    if (stages > per_cta) stages = per_cta;
+    if (stages > 28) stages = 28;
+    if (stages < 1) stages = 1;
+    plan.grid = grid;
+    plan.act_blocks = act_blocks;
+    plan.splits = (grid + nblocks - 1) / nblocks;  // typical K partitions of a column block
+    plan.stages = stages;
+    plan.smem_bytes = 16384 + 512 + (size_t)stages * stage_bytes(w.bits) + (size_t)act_blocks * 256 * rows;
+    plan.counter_bytes = align_up((size_t)nblocks * sizeof(unsigned int));
+    plan.partial_bytes = align_up((size_t)grid * 2 * rows * 128 * sizeof(float));
+    return plan;
+}
+
+template <int K, int CB>
+static cudaError_t launch_one(const GemvArgs& args, int grid, size_t smem, bool pdl, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemv_fused_kernel<K, CB>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, gemv_fused_kernel<K, CB>, args);
+}
+
+template <int CB>
+static cudaError_t launch_bits(const GemvArgs& a, int g, size_t smem, bool pdl, cudaStream_t s) {
+    switch (a.call.w.bits) {
+    case 1: return launch_one<1, CB>(a, g, smem, pdl, s);
+    case 2: return launch_one<2, CB>(a, g, smem, pdl, s);
+    case 3: return launch_one<3, CB>(a, g, smem, pdl, s);
+    case 4: return launch_one<4, CB>(a, g, smem, pdl, s);
+    case 5: return launch_one<5, CB>(a, g, smem, pdl, s);
+    case 6: return launch_one<6, CB>(a, g, smem, pdl, s);
+    case 7: return launch_one<7, CB>(a, g, smem, pdl, s);
+    case 8: return launch_one<8, CB>(a, g, smem, pdl, s);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_gemv(const LinearCall& call, const GemvPlan& plan, void* workspace,
+                        bool programmatic_launch, cudaStream_t stream) {
+    if (call.rows < 1 || call.rows > 8 || !workspace) return cudaErrorInvalidValue;
+    GemvArgs args{};
+    args.call = call;
+    args.stages = plan.stages;
+    args.act_blocks = plan.act_blocks;
+    args.counters = static_cast<unsigned int*>(workspace);
+    args.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + plan.counter_bytes);
+#ifdef ST_TIMELINE
+    if (const char* t = getenv("STRIX_TL")) args.timeline = (unsigned long long*)strtoull(t, nullptr, 16);
+#endif
+    switch (call.w.codebook) {
+    case CB_3INST: return launch_bits<CB_3INST>(args, plan.grid, plan.smem_bytes, programmatic_launch, stream);
+    case CB_MCG: return launch_bits<CB_MCG>(args, plan.grid, plan.smem_bytes, programmatic_launch, stream);
+    case CB_MUL1: return launch_bits<CB_MUL1>(args, plan.grid, plan.smem_bytes, programmatic_launch, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace st

@@ -1,0 +1,239 @@
+// Regrouping of the transport tile order, and the stage probes: dequantise, input
+// stages, output stages and the exact-order core.  The probes run the SAME device
+// functions as the fused kernels, so a bit-exact probe pins the production decoder
+// and transforms (the approach of the reference harness, docs/GPU_TESTS.md:97-109).
+#include "backend.h"
+#include "hadamard.cuh"
+#include "trellis_decode.cuh"
+
+namespace st {
+
+// ---- regroup: [I/16][N/16][W] -> [N/128][I/16][8][W], W = 8*bits words ------------
+__global__ void regroup_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst,
+                               int ktiles, int ntiles, int words) {
+    // One thread per word; consecutive threads walk consecutive destination words.
+    const long long total = (long long)ktiles * ntiles * words;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int word = (int)(i % words);
+        long long t = i / words;
+        const int sub = (int)(t % 8); t /= 8;
+        const int kt = (int)(t % ktiles);
+        const int nb = (int)(t / ktiles);
+        dst[i] = src[((long long)kt * ntiles + nb * 8 + sub) * words + word];
+    }
+}
+
+cudaError_t launch_regroup(const uint32_t* src, uint32_t* dst, int inputs, int outputs, int bits,
+                           cudaStream_t stream) {
+    const int ktiles = inputs / 16, ntiles = outputs / 16, words = 8 * bits;
+    const long long total = (long long)ktiles * ntiles * words;
+    const int block = 256;
+    const long long want = (total + block - 1) / block;
+    const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
+    regroup_kernel<<<grid, block, 0, stream>>>(src, dst, ktiles, ntiles, words);
+    return cudaGetLastError();
+}
+
+__device__ __forceinline__ const uint32_t* tile_ptr(const DeviceWeights& w, int kt, int nt) {
+    const int words = 8 * w.bits, ktiles = w.inputs / 16;
+    return w.packed + (((long long)(nt >> 3) * ktiles + kt) * 8 + (nt & 7)) * words;
+}
+
+// ---- dequantise: one warp per tile, through decode_tile_frag ------------------------
+template <int K, int CB>
+__global__ void dequantize_kernel(DeviceWeights w, uint16_t* __restrict__ q) {
+    const int lane = threadIdx.x & 31;
+    const int ktiles = w.inputs / 16, ntiles = w.outputs / 16;
+    const long long tiles = (long long)ktiles * ntiles;
+    for (long long t = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5); t < tiles;
+         t += (long long)gridDim.x * (blockDim.x >> 5)) {
+        const int kt = (int)(t / ntiles), nt = (int)(t % ntiles);
+        uint32_t frag[4];
+        decode_tile_frag<K, CB>(tile_ptr(w, kt, nt), lane, frag);
+        // frag order -> stream positions: frag[0]=(0,1) frag[2]=(2,3) frag[1]=(4,5) frag[3]=(6,7)
+        const uint32_t by_pos[4] = {frag[0], frag[2], frag[1], frag[3]};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint16_t v = (uint16_t)(by_pos[j >> 1] >> (16 * (j & 1)));
+            const int row = kt * 16 + frag_row(lane, j), col = nt * 16 + frag_col(lane, j);
+            q[(long long)row * w.outputs + col] = v;
+        }
+    }
+}
+
+template <int CB>
+static cudaError_t dequantize_bits(const DeviceWeights& w, uint16_t* q, int grid, cudaStream_t s) {
+    switch (w.bits) {
+    case 1: dequantize_kernel<1, CB><<<grid, 256, 0, s>>>(w, q); break;
+    case 2: dequantize_kernel<2, CB><<<grid, 256, 0, s>>>(w, q); break;
+    case 3: dequantize_kernel<3, CB><<<grid, 256, 0, s>>>(w, q); break;
+    case 4: dequantize_kernel<4, CB><<<grid, 256, 0, s>>>(w, q); break;
+    case 5: dequantize_kernel<5, CB><<<grid, 256, 0, s>>>(w, q); break;
+    case 6: dequantize_kernel<6, CB><<<grid, 256, 0, s>>>(w, q); break;
+    case 7: dequantize_kernel<7, CB><<<grid, 256, 0, s>>>(w, q); break;
+    case 8: dequantize_kernel<8, CB><<<grid, 256, 0, s>>>(w, q); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_dequantize(const DeviceWeights& w, uint16_t* q, cudaStream_t stream) {
+    const long long tiles = (long long)(w.inputs / 16) * (w.outputs / 16);
+    const long long want = (tiles + 7) / 8;
+    const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+    switch (w.codebook) {
+    case CB_3INST: return dequantize_bits<CB_3INST>(w, q, grid, stream);
+    case CB_MCG: return dequantize_bits<CB_MCG>(w, q, grid, stream);
+    case CB_MUL1: return dequantize_bits<CB_MUL1>(w, q, grid, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+// ---- input stages: one warp per (row, 128-block) -------------------------------------
+__global__ void input_stages_kernel(const float* __restrict__ x, long long x_stride,
+                                    const uint16_t* __restrict__ suh, int inputs, int rows,
+                                    uint16_t* scaled16, float* had32, uint16_t* core16) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = inputs / 128;
+    const long long groups = (long long)rows * blocks_per_row;
+    for (long long g = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5); g < groups;
+         g += (long long)gridDim.x * (blockDim.x >> 5)) {
+        const int row = (int)(g / blocks_per_row), begin = (int)(g % blocks_per_row) * 128;
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = begin + lane + 32 * j;
+            const __half h = scale_input(x[(long long)row * x_stride + c], suh[c]);
+            if (scaled16) scaled16[(long long)row * inputs + c] = __half_as_ushort(h);
+            v[j] = __half2float(h);
+        }
+        hadamard128_warp(v, lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const long long idx = (long long)row * inputs + begin + lane + 32 * j;
+            if (had32) had32[idx] = v[j];
+            if (core16) core16[idx] = __half_as_ushort(__float2half_rn(v[j]));
+        }
+    }
+}
+
+cudaError_t launch_input_stages(const DeviceWeights& w, const float* x, long long x_stride, int rows,
+                                uint16_t* scaled16, float* had32, uint16_t* core16,
+                                cudaStream_t stream) {
+    const long long groups = (long long)rows * (w.inputs / 128);
+    const long long want = (groups + 7) / 8;
+    const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+    input_stages_kernel<<<grid, 256, 0, stream>>>(x, x_stride, w.suh, w.inputs, rows, scaled16, had32,
+                                                  core16);
+    return cudaGetLastError();
+}
+
+// ---- output stages: fold split planes ascending from +0, H128, svh, bias, alpha/beta ---
+__global__ void output_stages_kernel(const float* __restrict__ core, int splits, int rows,
+                                     const uint16_t* __restrict__ svh, const float* __restrict__ bias,
+                                     int outputs, float* y, long long y_stride, float alpha, float beta) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = outputs / 128;
+    const long long groups = (long long)rows * blocks_per_row;
+    for (long long g = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5); g < groups;
+         g += (long long)gridDim.x * (blockDim.x >> 5)) {
+        const int row = (int)(g / blocks_per_row), begin = (int)(g % blocks_per_row) * 128;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < splits; ++s)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                v[j] = __fadd_rn(v[j], core[((long long)s * rows + row) * outputs + begin + lane + 32 * j]);
+        hadamard128_warp(v, lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = begin + lane + 32 * j;
+            float* out = y + (long long)row * y_stride + c;
+            *out = finish_output(v[j], svh[c], bias, c, alpha, beta, out);
+        }
+    }
+}
+
+cudaError_t launch_output_stages(const DeviceWeights& w, const float* core, int splits, int rows,
+                                 float* y, long long y_stride, float alpha, float beta,
+                                 cudaStream_t stream) {
+    const long long groups = (long long)rows * (w.outputs / 128);
+    const long long want = (groups + 7) / 8;
+    const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+    output_stages_kernel<<<grid, 256, 0, stream>>>(core, splits, rows, w.svh, w.bias, w.outputs, y,
+                                                   y_stride, alpha, beta);
+    return cudaGetLastError();
+}
+
+// ---- exact-order core: a warp owns a 16-column tile band and walks K ascending ---------
+// Lane t accumulates output column (t%16) for rows (t/16), (t/16)+2, ...; each k-tile is
+// decoded once by the warp, transposed through shared memory, then consumed in ascending
+// input order with one fma per (row, input).
+template <int K, int CB>
+__global__ void core_exact_kernel(DeviceWeights w, const uint16_t* __restrict__ a16, int rows,
+                                  float* __restrict__ core) {
+    __shared__ uint16_t tile[8][16][16];  // [warp][input row][output col]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nt = blockIdx.x * 8 + warp;
+    if (nt >= w.outputs / 16) return;
+    const int col = lane & 15, row0 = lane >> 4;
+    float acc[32];  // rows row0, row0+2, ... (up to 64 rows)
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    for (int kt = 0; kt < w.inputs / 16; ++kt) {
+        uint32_t frag[4];
+        decode_tile_frag<K, CB>(tile_ptr(w, kt, nt), lane, frag);
+        const uint32_t by_pos[4] = {frag[0], frag[2], frag[1], frag[3]};
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            tile[warp][frag_row(lane, j)][frag_col(lane, j)] = (uint16_t)(by_pos[j >> 1] >> (16 * (j & 1)));
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int r = row0 + 2 * i;
+            if (r < rows) {
+                for (int k = 0; k < 16; ++k) {
+                    const float a = half_bits_to_float(a16[(long long)r * w.inputs + kt * 16 + k]);
+                    acc[i] = __fmaf_rn(a, half_bits_to_float(tile[warp][k][col]), acc[i]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const int r = row0 + 2 * i;
+        if (r < rows) core[(long long)r * w.outputs + nt * 16 + col] = acc[i];
+    }
+}
+
+template <int CB>
+static cudaError_t core_exact_bits(const DeviceWeights& w, const uint16_t* a, int rows, float* c,
+                                   cudaStream_t s) {
+    const int grid = (w.outputs / 16 + 7) / 8;
+    switch (w.bits) {
+    case 1: core_exact_kernel<1, CB><<<grid, 256, 0, s>>>(w, a, rows, c); break;
+    case 2: core_exact_kernel<2, CB><<<grid, 256, 0, s>>>(w, a, rows, c); break;
+    case 3: core_exact_kernel<3, CB><<<grid, 256, 0, s>>>(w, a, rows, c); break;
+    case 4: core_exact_kernel<4, CB><<<grid, 256, 0, s>>>(w, a, rows, c); break;
+    case 5: core_exact_kernel<5, CB><<<grid, 256, 0, s>>>(w, a, rows, c); break;
+    case 6: core_exact_kernel<6, CB><<<grid, 256, 0, s>>>(w, a, rows, c); break;
+    case 7: core_exact_kernel<7, CB><<<grid, 256, 0, s>>>(w, a, rows, c); break;
+    case 8: core_exact_kernel<8, CB><<<grid, 256, 0, s>>>(w, a, rows, c); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_core_exact(const DeviceWeights& w, const uint16_t* core16, int rows, float* core_out,
+                              cudaStream_t stream) {
+    if (rows < 1 || rows > 64) return cudaErrorInvalidValue;
+    switch (w.codebook) {
+    case CB_3INST: return core_exact_bits<CB_3INST>(w, core16, rows, core_out, stream);
+    case CB_MCG: return core_exact_bits<CB_MCG>(w, core16, rows, core_out, stream);
+    case CB_MUL1: return core_exact_bits<CB_MUL1>(w, core16, rows, core_out, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace st

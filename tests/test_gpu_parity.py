@@ -1,0 +1,234 @@
+"""GPU parity tests: every call goes through the C ABI of libstrix_trellis.so."""
+import hashlib
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle, trellis_ref as ref
+from strix_trellis_b200 import native as N, synthetic
+from gpu_util import dev, gate, host
+
+pytestmark = pytest.mark.gpu
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    from strix_trellis_b200.runtime import Context
+    c = Context(0)
+    yield c
+    assert c.device_status() == 0
+    c.close()
+
+
+@pytest.fixture(scope="module")
+def grid(golden_dir):
+    meta = json.loads((golden_dir / "grid.json").read_text())
+    return meta, np.load(golden_dir / "grid_ref.npz")
+
+
+def test_stage_probes_bit_exact_on_reference_grid(ctx, grid):
+    """Decoded Q, scaled fp16, input H128, core input, exact-order core and the output
+    stages must equal the reference's checkpoints bit for bit (all 48 grid cases)."""
+    meta, outs = grid
+    for case in meta["cases"]:
+        layer, x, old, _ = synthetic.grid_case(case["codebook"], case["bits"], case["wide"], meta["rows"])
+        for use_blob in (False, True):
+            w = ctx.prepare(layer, use_blob=use_blob)
+            assert sha(host(w.dequantize())) == case["q"], case["name"]
+            if use_blob:
+                w.close()
+                continue
+            scaled, had, core_in = w.input_stages(dev(x))
+            assert sha(host(scaled)) == case["scaled"], case["name"]
+            assert sha(host(had)) == case["inh"], case["name"]
+            assert sha(host(core_in)) == case["a"], case["name"]
+            core = w.core_exact(core_in)
+            assert sha(host(core)) == case["core"], case["name"]
+            y = w.output_stages(core)
+            assert sha(host(y)) == case["ref"], case["name"]
+            # output stages on the oracle's core, with alpha/beta and an old output
+            for alpha, beta in [(-0.75, 0.25), (0.0, -0.5), (1.0, -0.0)]:
+                yy = dev(old.copy())
+                w.output_stages(dev(outs[case["name"] + ":core"]), alpha, beta, yy)
+                want = c_oracle.output_stages(outs[case["name"] + ":core"], layer.svh, layer.bias, alpha, beta, old)["output"]
+                assert host(yy).tobytes() == want.tobytes(), (case["name"], alpha, beta)
+            w.close()
+
+
+def test_output_stage_folds_split_planes_in_order(ctx):
+    layer = synthetic.make_layer(128, 256, 4, seed=11, bias=True)
+    w = ctx.prepare(layer)
+    rng = np.random.default_rng(3)
+    planes = (rng.normal(size=(5, 3, 256)) * 10.0 ** rng.integers(-3, 4, (5, 3, 256))).astype(np.float32)
+    acc = np.zeros((3, 256), np.float32)
+    for s in range(5):
+        acc = acc + planes[s]
+    want = c_oracle.output_stages(acc, layer.svh, layer.bias)["output"]
+    assert host(w.output_stages(dev(planes))).tobytes() == want.tobytes()
+    w.close()
+
+
+@pytest.mark.parametrize("rows", [1, 2, 3, 8])
+def test_gemv_grid_all_rates_and_codebooks(ctx, grid, rows):
+    meta, outs = grid
+    for case in meta["cases"]:
+        layer, x, old, _ = synthetic.grid_case(case["codebook"], case["bits"], case["wide"], meta["rows"])
+        w = ctx.prepare(layer)
+        y = w.gemv(dev(x[:rows]))
+        gate(host(y), outs[case["name"]][:rows], case["name"])
+        w.close()
+
+
+def test_gemv_rank1_alpha_beta_and_poisoned_output(ctx, grid):
+    meta, outs = grid
+    for case in meta["cases"][::5]:
+        layer, x, old, _ = synthetic.grid_case(case["codebook"], case["bits"], case["wide"], meta["rows"])
+        w = ctx.prepare(layer)
+        want = outs[case["name"]]
+        y1 = w.gemv(dev(x[0]))
+        assert y1.shape == (layer.outputs,)
+        gate(host(y1)[None], want[:1], case["name"])
+        for alpha, beta in [(-0.75, 0.25), (0.0, -0.5)]:
+            y = dev(old[:4].copy())
+            w.gemv(dev(x[:4]), y, alpha, beta)
+            gate(host(y), ref.apply_alpha_beta(want[:4], alpha, beta, old[:4]), case["name"])
+        for beta in (0.0, -0.0):  # beta == 0 must never read the old output
+            y = torch.full((4, layer.outputs), float("nan"), device="cuda")
+            w.gemv(dev(x[:4]), y, 1.0, beta)
+            gate(host(y), want[:4], case["name"])
+        w.close()
+
+
+def test_empty_call_validates_and_launches_nothing(ctx):
+    layer = synthetic.make_layer(128, 128, 4, seed=5)
+    w = ctx.prepare(layer)
+    x = torch.empty((0, 128), device="cuda")
+    y = torch.empty((0, 128), device="cuda")
+    assert w.workspace_bytes(x, y) == 0
+    w.gemv(x, y)
+    w.gemm(x, y)
+    w.close()
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 5, 6])
+@pytest.mark.parametrize("shape", [(4096, 4096), (5120, 5120), (1152, 4096), (4096, 14336)])
+def test_gemv_benchmark_shapes(ctx, bits, shape):
+    inputs, outputs = shape
+    layer = synthetic.make_layer(inputs, outputs, bits, seed=synthetic.BASE_SEED + bits)
+    w = ctx.prepare(layer)
+    x = synthetic.make_activations(8, inputs, seed=synthetic.BASE_SEED + 100 + bits)
+    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, None, bits, 2, x)
+    for rows in (1, 2, 4, 8):
+        gate(host(w.gemv(dev(x[:rows]))), want[:rows], f"k{bits} {shape} r{rows}")
+    w.close()
+
+
+def test_config1_against_reference_golden(ctx, golden_dir):
+    meta = json.loads((golden_dir / "config1.json").read_text())
+    gold = np.load(golden_dir / "config1.npz")
+    layer = synthetic.make_layer(4096, 4096, 4, seed=meta["seed"])
+    x = synthetic.make_activations(1, 4096, seed=meta["x_seed"])
+    w = ctx.prepare(layer)
+    assert sha(host(w.dequantize())) == meta["q"]
+    _, _, core_in = w.input_stages(dev(x))
+    assert sha(host(core_in)) == meta["a"]
+    core = w.core_exact(core_in)
+    assert sha(host(core)) == meta["core"]           # reference accumulation order reproduced
+    assert sha(host(w.output_stages(core))) == meta["ref"]
+    gate(host(w.gemv(dev(x))), gold["ref"], "config1 fused")
+    w.close()
+
+
+@pytest.mark.parametrize("rows", [9, 16, 17, 32])
+def test_gemm_small_rows(ctx, grid, rows):
+    meta, outs = grid
+    for case in meta["cases"][::7]:
+        layer, _, _, _ = synthetic.grid_case(case["codebook"], case["bits"], case["wide"], meta["rows"])
+        x = synthetic.make_activations(rows, layer.inputs, seed=77)
+        w = ctx.prepare(layer)
+        want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, layer.bits, case["codebook"], x)
+        gate(host(w.gemm(dev(x))), want, case["name"])
+        w.close()
+
+
+def test_plan_submit_and_graph_replay(ctx):
+    layer = synthetic.make_layer(4096, 1024, 5, seed=21, bias=True)
+    w = ctx.prepare(layer)
+    x = dev(synthetic.make_activations(4, 4096, seed=22))
+    y = torch.zeros((4, 1024), device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        plan = w.plan(x, y, N.OP_GEMV, stream=stream)
+        plan.submit()
+        stream.synchronize()
+        want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, 5, 2, host(x))
+        gate(host(y), want, "plan")
+        first = host(y).copy()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            plan.submit()
+        for trial in range(3):
+            x2 = synthetic.make_activations(4, 4096, seed=30 + trial)
+            x.copy_(dev(x2))
+            y.fill_(float("nan"))
+            graph.replay()
+            stream.synchronize()
+            gate(host(y), c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, 5, 2, x2), "graph")
+        # same inputs -> same bits, run to run
+        x.copy_(dev(synthetic.make_activations(4, 4096, seed=22)))
+        plan.submit()
+        stream.synchronize()
+        assert host(y).tobytes() == first.tobytes()
+        del graph
+        assert N.load().strix_weights_destroy(w.handle) == N.INVALID_ARGUMENT  # retained by the plan
+        plan.close()
+    w.close()
+
+
+def test_rejections_with_the_real_driver(ctx):
+    """Host memory, short and misaligned workspace, aliasing: rejected before any launch
+    (the reference's real-driver negative cases, tests/gpu_runtime.hip:189-219)."""
+    import ctypes as C
+    # K so deep that the split-K fold needs global scratch (more partitions than a cluster holds)
+    layer = synthetic.make_layer(34816 * 2, 128, 2, seed=9)
+    w = ctx.prepare(layer)
+    lib = N.load()
+    x = dev(synthetic.make_activations(8, 34816 * 2))
+    y = torch.full((8, 128), 7.0, device="cuda")
+    need = w.workspace_bytes(x, y)
+    assert need > 0
+    ws = torch.empty(need + 512, dtype=torch.uint8, device="cuda")
+    sd = N.stream_desc(torch.cuda.current_stream().cuda_stream)
+
+    def status(d):
+        return lib.strix_gemv(ctx.handle, C.byref(d), C.byref(sd))
+
+    d = w.matmul_desc(x, y, workspace=ws[: need - 256])
+    assert status(d) == N.INSUFFICIENT_BUFFER
+    d = w.matmul_desc(x, y, workspace=ws[4: need + 4])
+    assert status(d) == N.INVALID_ARGUMENT
+    d = w.matmul_desc(x, x[:, :128], workspace=ws)
+    assert status(d) in (N.INVALID_ARGUMENT, N.UNSUPPORTED_FORMAT)
+    hx = torch.zeros((8, 34816 * 2)).pin_memory()
+    d = w.matmul_desc(x, y, workspace=ws)
+    d.input.data = hx.data_ptr()
+    assert status(d) == N.INVALID_ARGUMENT
+    d = w.matmul_desc(x, y, workspace=ws)
+    d.alpha = float("inf")
+    assert status(d) == N.INVALID_ARGUMENT
+    d = w.matmul_desc(x, y, workspace=ws)
+    d.input.dtype = 1
+    assert status(d) == N.UNSUPPORTED_FORMAT
+    torch.cuda.synchronize()
+    assert (host(y) == 7.0).all()  # nothing ran
+    # and the deep-K global-scratch path itself is correct
+    got = w.gemv(x, workspace=ws)
+    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, None, 2, 2, host(x))
+    gate(host(got), want, "deep K global fold")
+    w.close()
