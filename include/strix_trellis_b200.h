@@ -62,6 +62,28 @@ strix_status strix_b200_device_status(strix_context context, uint32_t *out_bits)
  * or writes anything.  No counterpart in the reference. */
 strix_status strix_b200_set_programmatic_launch(strix_context context, uint32_t enabled);
 
+/* strix_gemv for callers that may not allocate.  It has no counterpart in the reference.
+ *
+ * Some engines hand every byte of device memory to their own arena when they start and
+ * never call the CUDA allocator again: a cudaMalloc in the middle of a decode loop
+ * serialises the whole device, and with the arena holding everything it would simply
+ * fail.  Such a caller has nowhere to take the GEMV's split-K scratch from.  This entry
+ * point needs none: its arrival counters and partial planes sit in a fixed array of
+ * STRIX_B200_NOALLOC_SCRATCH_BYTES inside the library image (every GPU that loads the
+ * library holds that array until the process exits).  It calls no allocating routine.
+ *
+ * Same operator and same results as strix_gemv (rows 0..8); desc->workspace must be
+ * NULL/0; tensors are still the caller's.  Limits: outputs <= STRIX_B200_NOALLOC_MAX_OUTPUTS
+ * and at most 192 SMs; anything larger returns STRIX_ERROR_INSUFFICIENT_BUFFER.
+ * The first call on a device looks up the array's device address (one runtime query);
+ * make that first call before starting any stream capture.  All calls on a device share
+ * the one array, so two calls that can overlap on the GPU (different streams without an
+ * ordering between them) race; keep them in one stream or order them with events. */
+#define STRIX_B200_NOALLOC_MAX_OUTPUTS UINT64_C(524288)
+#define STRIX_B200_NOALLOC_SCRATCH_BYTES UINT64_C(1589248)
+strix_status strix_b200_gemv_noalloc(strix_context context, const strix_matmul_desc *desc,
+                                     const strix_stream *stream);
+
 #ifdef __cplusplus
 }
 #endif

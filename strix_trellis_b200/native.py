@@ -199,6 +199,7 @@ PROTOTYPES = {
     "strix_b200_gemv_splits": (C.c_int, [vp, vp, u32, P(u32)]),
     "strix_b200_device_status": (C.c_int, [vp, P(u32)]),
     "strix_b200_set_programmatic_launch": (C.c_int, [vp, u32]),
+    "strix_b200_gemv_noalloc": (C.c_int, [vp, P(MatmulDesc), P(Stream)]),
 }
 
 _LIB = None
