@@ -41,13 +41,4 @@ cudaError_t launch_gemm_chunked(const LinearCall& call, int sm_count, void* work
     return cudaSuccess;
 }
 
-GemmPlan plan_gemm(const DeviceWeights& w, int rows, int sm_count) {
-    return plan_gemm_chunked(w, rows, sm_count);
-}
-
-cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* workspace,
-                        cudaStream_t stream) {
-    return launch_gemm_chunked(call, plan.sm_count, workspace, stream);
-}
-
 }  // namespace st

@@ -1,0 +1,352 @@
+// Prefill GEMM (rows > 8) on the 5th-generation tensor cores: tcgen05.mma with fp32
+// accumulators in tensor memory, trellis tiles decoded on the fly by producer warps
+// into the swizzled K-major shared-memory layout the MMA reads, and the output stages
+// (H128, svh, bias, alpha/beta) fused into the epilogue.  It stands in for the reference's
+// input_transform + wmma tiled core + fused output epilogue (src/wmma_tiled.hip:87-269,
+// src/gemm.hip:15-76, src/backend.hip:121-140).
+//
+// Two launches: (1) input stages, writing the RN16 core input as pre-swizzled
+// [128 rows x 64 k] tiles so that each tile is ONE contiguous 16 KB bulk copy;
+// (2) the persistent GEMM kernel, one CTA per SM, CTA tile = 256 rows x 128 columns
+// (two 128-row accumulators share every decoded weight stage), K stepped by 64.
+//   warp 0      A producer  : cp.async.bulk of the two A tiles of a stage
+//   warp 1      MMA issuer  : tcgen05.mma (one thread), tcgen05.commit to the barriers
+//   warps 2-5   epilogue    : tcgen05.ld -> shared staging -> H128 by warp shuffles -> y
+//   warps 6-13  decoders    : trellis tiles -> B stage in shared memory
+// TMEM: 2 tile buffers x (2 x 128) columns, so the epilogue of one tile overlaps the
+// main loop of the next.  Every wait is bounded.
+#include <cstdlib>
+
+#include "backend.h"
+#include "hadamard.cuh"
+#include "sync_primitives.cuh"
+#include "tcgen05.cuh"
+#include "trellis_decode.cuh"
+
+namespace st {
+
+namespace {
+constexpr int kBM = 128, kMT = 2, kBN = 128, kBK = 64;
+constexpr int kStagesTc = 3;
+constexpr int kTileBytes = kBM * kBK * 2;                      // 16 KB
+constexpr int kStageBytesTc = (kMT + 1) * kTileBytes;          // A0, A1, B
+constexpr int kDecodeWarps = 8, kEpiWarps = 4;
+constexpr int kThreadsTc = (2 + kEpiWarps + kDecodeWarps) * 32;
+constexpr int kStagingStride = 129;                            // floats per staged row
+constexpr int kStagingBytes = 32 * kStagingStride * 4;         // per epilogue warp
+constexpr size_t kSmemTc = 1024 + (size_t)kStagesTc * kStageBytesTc + (size_t)kEpiWarps * kStagingBytes + 256;
+constexpr uint32_t kTmemCols = 512;
+
+struct GemmArgs {
+    LinearCall call;
+    const unsigned char* a_tiles;  // [M/128 padded][I/64][16 KB]
+    int m_pairs;                   // ceil(rows / 256)
+};
+}  // namespace
+
+// ---- launch 1: input stages into pre-swizzled A tiles ------------------------------------
+__global__ void input_tiles_kernel(const float* __restrict__ x, long long x_stride,
+                                   const uint16_t* __restrict__ suh, int inputs, int rows, int rows_padded,
+                                   unsigned char* __restrict__ a_tiles) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = inputs / 128, kt64 = inputs / 64;
+    const long long groups = (long long)rows_padded * blocks_per_row;
+    for (long long g = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5); g < groups;
+         g += (long long)gridDim.x * (blockDim.x >> 5)) {
+        const int row = (int)(g / blocks_per_row), blk = (int)(g % blocks_per_row);
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (row < rows) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = blk * 128 + lane + 32 * j;
+                v[j] = __half2float(scale_input(x[(long long)row * x_stride + c], suh[c]));
+            }
+            hadamard128_warp(v, lane);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = blk * 128 + lane + 32 * j;  // input index
+            unsigned char* tile = a_tiles + ((size_t)(row >> 7) * kt64 + (k >> 6)) * kTileBytes;
+            *reinterpret_cast<__half*>(tile + sw128_offset(row & 127, k & 63)) = __float2half_rn(v[j]);
+        }
+    }
+}
+
+// ---- launch 2: the GEMM ---------------------------------------------------------------------
+template <int K, int CB>
+__global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs args) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const LinearCall& c = args.call;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kt64 = c.w.inputs / 64, ktiles16 = c.w.inputs / 16;
+    const int nblocks = c.w.outputs / 128;
+    const long long tiles = (long long)nblocks * args.m_pairs;
+
+    unsigned char* ring = smem;
+    float* staging = reinterpret_cast<float*>(ring + (size_t)kStagesTc * kStageBytesTc);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(staging) +
+                                                 (size_t)kEpiWarps * kStagingBytes);
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+    const uint32_t full_a = smem_u32(bars), full_b = smem_u32(bars + kStagesTc),
+                   empty = smem_u32(bars + 2 * kStagesTc), tmem_full = smem_u32(bars + 3 * kStagesTc),
+                   tmem_empty = smem_u32(bars + 3 * kStagesTc + 2);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStagesTc; ++i) {
+            mbar_init(full_a + 8 * i, 1);
+            mbar_init(full_b + 8 * i, kDecodeWarps);
+            mbar_init(empty + 8 * i, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(tmem_full + 8 * i, 1);
+            mbar_init(tmem_empty + 8 * i, kEpiWarps);
+        }
+        mbar_fence_init();
+        s_abort = 0;
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), kTmemCols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = s_tmem_base;
+
+    if (warp == 0) {
+        // ---- A producer ---------------------------------------------------------------
+        if (lane == 0) {
+            long long it = 0;
+            for (long long t = blockIdx.x; t < tiles && !s_abort; t += gridDim.x) {
+                const int mp = (int)(t % args.m_pairs);
+                for (int ks = 0; ks < kt64; ++ks, ++it) {
+                    const int st = (int)(it % kStagesTc);
+                    if (it >= kStagesTc &&
+                        !mbar_wait(empty + 8 * st, (uint32_t)((it / kStagesTc) - 1) & 1, c.status, kTimeoutTensorPipe)) {
+                        s_abort = 1;
+                        break;
+                    }
+                    unsigned char* dst = ring + (size_t)st * kStageBytesTc;
+                    mbar_expect_tx(full_a + 8 * st, kMT * kTileBytes);
+#pragma unroll
+                    for (int mt = 0; mt < kMT; ++mt)
+                        bulk_load(smem_u32(dst + mt * kTileBytes),
+                                  args.a_tiles + ((size_t)(mp * kMT + mt) * kt64 + ks) * kTileBytes, kTileBytes,
+                                  full_a + 8 * st);
+                }
+            }
+            // Never leave with a copy still landing in this CTA's shared memory.
+            for (long long i = (it > kStagesTc ? it - kStagesTc : 0); i < it; ++i)
+                mbar_wait(full_a + 8 * (int)(i % kStagesTc), (uint32_t)(i / kStagesTc) & 1, c.status, kTimeoutDrain);
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ---------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_f16_f32(kBM, kBN);
+            long long it = 0;
+            int local_tile = 0;
+            for (long long t = blockIdx.x; t < tiles && !s_abort; t += gridDim.x, ++local_tile) {
+                const int buf = local_tile & 1;
+                if (local_tile >= 2 &&
+                    !mbar_wait(tmem_empty + 8 * buf, (uint32_t)((local_tile >> 1) - 1) & 1, c.status, kTimeoutTensorPipe)) {
+                    s_abort = 1;
+                    break;
+                }
+                tc_fence_after_sync();
+                for (int ks = 0; ks < kt64 && !s_abort; ++ks, ++it) {
+                    const int st = (int)(it % kStagesTc);
+                    const uint32_t par = (uint32_t)(it / kStagesTc) & 1;
+                    if (!mbar_wait(full_a + 8 * st, par, c.status, kTimeoutTensorPipe) ||
+                        !mbar_wait(full_b + 8 * st, par, c.status, kTimeoutTensorPipe)) {
+                        s_abort = 1;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t base = smem_u32(ring + (size_t)st * kStageBytesTc);
+                    const uint64_t bdesc = umma_desc_k_major_sw128(base + kMT * kTileBytes);
+#pragma unroll
+                    for (int mt = 0; mt < kMT; ++mt) {
+                        const uint64_t adesc = umma_desc_k_major_sw128(base + mt * kTileBytes);
+#pragma unroll
+                        for (int k4 = 0; k4 < kBK / 16; ++k4)  // +32 bytes per 16-element K step
+                            umma_f16(tmem_base + buf * (kMT * kBN) + mt * kBN, adesc + 2 * k4, bdesc + 2 * k4, idesc,
+                                     (ks | k4) != 0);
+                    }
+                    umma_commit(empty + 8 * st);  // stage reusable once these MMAs have read it
+                }
+                umma_commit(tmem_full + 8 * buf);  // accumulators of this tile complete
+            }
+        }
+    } else if (warp < 2 + kEpiWarps) {
+        // ---- epilogue -------------------------------------------------------------------
+        const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. +31
+        float* stage = staging + (size_t)(warp - 2) * 32 * kStagingStride;
+        int local_tile = 0;
+        for (long long t = blockIdx.x; t < tiles; t += gridDim.x, ++local_tile) {
+            const int buf = local_tile & 1;
+            const int nb = (int)(t / args.m_pairs), mp = (int)(t % args.m_pairs);
+            if (s_abort || !mbar_wait(tmem_full + 8 * buf, (uint32_t)(local_tile >> 1) & 1, c.status, kTimeoutTensorPipe)) {
+                s_abort = 1;
+                break;
+            }
+            tc_fence_after_sync();
+            for (int mt = 0; mt < kMT; ++mt) {
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (kMT * kBN) + mt * kBN;
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + ch * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) stage[lane * kStagingStride + ch * 32 + j] = __uint_as_float(r[j]);
+                }
+                if (mt == kMT - 1) {  // both accumulators read: hand the TMEM buffer back
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tmem_empty + 8 * buf);
+                }
+                __syncwarp();
+                const int row_base = (mp * kMT + mt) * kBM + quarter * 32;
+                for (int r = 0; r < 32; ++r) {
+                    const int row = row_base + r;
+                    if (row >= c.rows) break;
+                    float v[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[j] = stage[r * kStagingStride + lane + 32 * j];
+                    hadamard128_warp(v, lane);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int cidx = nb * 128 + lane + 32 * j;
+                        float* out = c.y + (long long)row * c.y_stride + cidx;
+                        *out = finish_output(v[j], c.w.svh[cidx], c.w.bias, cidx, c.alpha, c.beta, out);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---- decoders: trellis tiles -> swizzled K-major B stage -------------------------------
+        const int d = warp - (2 + kEpiWarps);  // column tile of the 128-column block
+        const LaneGeom<K> geom(lane);
+        const int n0 = d * 16 + (lane >> 2), kq = 2 * (lane & 3);
+        long long it = 0;
+        for (long long t = blockIdx.x; t < tiles && !s_abort; t += gridDim.x) {
+            const int nb = (int)(t / args.m_pairs);
+            const uint32_t* column = c.w.packed + (((size_t)nb * ktiles16) * 8 + d) * (8 * K);
+            for (int ks = 0; ks < kt64; ++ks, ++it) {
+                const int st = (int)(it % kStagesTc);
+                if (it >= kStagesTc &&
+                    !mbar_wait(empty + 8 * st, (uint32_t)((it / kStagesTc) - 1) & 1, c.status, kTimeoutTensorPipe)) {
+                    s_abort = 1;
+                    break;
+                }
+                unsigned char* bt = ring + (size_t)st * kStageBytesTc + kMT * kTileBytes;
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    uint32_t frag[4];
+                    decode_tile_frag<K, CB>(column + (size_t)(ks * 4 + k4) * 8 * (8 * K), geom, frag);
+                    const int k = k4 * 16 + kq;
+                    // frag[0]: (n0, k..k+1)  frag[2]: (n0, k+8..)  frag[1]: (n0+8, k..)  frag[3]: (n0+8, k+8..)
+                    *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0, k)) = frag[0];
+                    *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0, k + 8)) = frag[2];
+                    *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0 + 8, k)) = frag[1];
+                    *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0 + 8, k + 8)) = frag[3];
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_b + 8 * st);
+            }
+        }
+    }
+
+    // ---- common exit: nobody leaves before every role is done, then TMEM is returned ------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+static bool tc_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("STRIX_B200_GEMM");
+        return !(e && e[0] == 'c');  // "chunked" forces the 8-row GEMV route (measurement switch)
+    }();
+    return on;
+}
+
+GemmPlan plan_gemm_chunked(const DeviceWeights& w, int rows, int sm_count);
+cudaError_t launch_gemm_chunked(const LinearCall& call, int sm_count, void* workspace, cudaStream_t stream);
+
+GemmPlan plan_gemm(const DeviceWeights& w, int rows, int sm_count) {
+    if (!tc_enabled() || rows < 64) return plan_gemm_chunked(w, rows, sm_count);
+    GemmPlan plan{};
+    const int m_pairs = (rows + kBM * kMT - 1) / (kBM * kMT);
+    plan.act_bytes = (size_t)m_pairs * kMT * kBM * w.inputs * 2;
+    plan.workspace_bytes = align_up(plan.act_bytes);
+    plan.tile_m = kBM * kMT;
+    plan.tile_n = kBN;
+    plan.sm_count = sm_count;
+    plan.tensor_core = true;
+    return plan;
+}
+
+template <int K, int CB>
+static cudaError_t launch_tc(const GemmArgs& args, int grid, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<K, CB>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    gemm_tc_kernel<K, CB><<<grid, kThreadsTc, kSmemTc, stream>>>(args);
+    return cudaGetLastError();
+}
+
+template <int CB>
+static cudaError_t launch_tc_bits(const GemmArgs& a, int grid, cudaStream_t s) {
+    switch (a.call.w.bits) {
+    case 1: return launch_tc<1, CB>(a, grid, s);
+    case 2: return launch_tc<2, CB>(a, grid, s);
+    case 3: return launch_tc<3, CB>(a, grid, s);
+    case 4: return launch_tc<4, CB>(a, grid, s);
+    case 5: return launch_tc<5, CB>(a, grid, s);
+    case 6: return launch_tc<6, CB>(a, grid, s);
+    case 7: return launch_tc<7, CB>(a, grid, s);
+    case 8: return launch_tc<8, CB>(a, grid, s);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* workspace, cudaStream_t stream) {
+    if (!plan.tensor_core) return launch_gemm_chunked(call, plan.sm_count, workspace, stream);
+    if (!workspace) return cudaErrorInvalidValue;
+    const int m_pairs = (call.rows + kBM * kMT - 1) / (kBM * kMT);
+    const int rows_padded = m_pairs * kBM * kMT;
+    {
+        const long long groups = (long long)rows_padded * (call.w.inputs / 128);
+        const long long want = (groups + 7) / 8;
+        const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+        input_tiles_kernel<<<grid, 256, 0, stream>>>(call.x, call.x_stride, call.w.suh, call.w.inputs, call.rows,
+                                                     rows_padded, static_cast<unsigned char*>(workspace));
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    GemmArgs args{};
+    args.call = call;
+    args.a_tiles = static_cast<const unsigned char*>(workspace);
+    args.m_pairs = m_pairs;
+    const long long tiles = (long long)(call.w.outputs / 128) * m_pairs;
+    const int grid = (int)(tiles < plan.sm_count ? tiles : plan.sm_count);
+    switch (call.w.codebook) {
+    case CB_3INST: return launch_tc_bits<CB_3INST>(args, grid, stream);
+    case CB_MCG: return launch_tc_bits<CB_MCG>(args, grid, stream);
+    case CB_MUL1: return launch_tc_bits<CB_MUL1>(args, grid, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace st

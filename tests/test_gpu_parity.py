@@ -157,6 +157,34 @@ def test_gemm_small_rows(ctx, grid, rows):
         w.close()
 
 
+@pytest.mark.parametrize("rows", [64, 128, 200, 256, 300])
+def test_gemm_tensor_core_small_layers(ctx, grid, rows):
+    """Rows >= 64 take the tcgen05 kernel: every rate and codebook, ragged row counts."""
+    meta, outs = grid
+    for case in meta["cases"][::3]:
+        layer, _, _, _ = synthetic.grid_case(case["codebook"], case["bits"], case["wide"], meta["rows"])
+        x = synthetic.make_activations(rows, layer.inputs, seed=78)
+        old = synthetic.rng_for(79).normal(0, 0.3, (rows, layer.outputs)).astype(np.float32)
+        w = ctx.prepare(layer)
+        want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, layer.bits, case["codebook"], x)
+        gate(host(w.gemm(dev(x))), want, case["name"])
+        y = dev(old.copy())
+        w.gemm(dev(x), y, alpha=-0.75, beta=0.25)
+        gate(host(y), ref.apply_alpha_beta(want, -0.75, 0.25, old), case["name"] + " alpha/beta")
+        w.close()
+
+
+@pytest.mark.parametrize("bits", [4, 5, 6])
+def test_gemm_tensor_core_prefill_shape(ctx, bits):
+    """4096 -> 1536 slice of the benchmark's fused-QKV-like layer, 512 token rows."""
+    layer = synthetic.make_layer(4096, 1536, bits, seed=90 + bits)
+    x = synthetic.make_activations(512, 4096, seed=91)
+    w = ctx.prepare(layer)
+    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, None, bits, 2, x)
+    gate(host(w.gemm(dev(x))), want, f"prefill k{bits}")
+    w.close()
+
+
 def test_plan_submit_and_graph_replay(ctx):
     layer = synthetic.make_layer(4096, 1024, 5, seed=21, bias=True)
     w = ctx.prepare(layer)
