@@ -12,7 +12,8 @@
 //   warp 0      A producer  : cp.async.bulk of the two A tiles of a stage
 //   warp 1      MMA issuer  : tcgen05.mma (one thread), tcgen05.commit to the barriers
 //   warps 2-5   epilogue    : tcgen05.ld -> shared staging -> H128 by warp shuffles -> y
-//   warps 6-13  decoders    : trellis tiles -> B stage in shared memory
+//   warps 6-21  decoders    : trellis tiles -> B stage in shared memory; two groups of
+//                             eight take alternate stages, next stage's words prefetched
 // TMEM: 2 tile buffers x (2 x 128) columns, so the epilogue of one tile overlaps the
 // main loop of the next.  Every wait is bounded.
 #include <cstdlib>
@@ -30,7 +31,7 @@ constexpr int kBM = 128, kMT = 2, kBN = 128, kBK = 64;
 constexpr int kStagesTc = 3;
 constexpr int kTileBytes = kBM * kBK * 2;                      // 16 KB
 constexpr int kStageBytesTc = (kMT + 1) * kTileBytes;          // A0, A1, B
-constexpr int kDecodeWarps = 8, kEpiWarps = 4;
+constexpr int kDecodeWarps = 16, kEpiWarps = 4;  // two decode groups leapfrog over the stages
 constexpr int kThreadsTc = (2 + kEpiWarps + kDecodeWarps) * 32;
 constexpr int kStagingStride = 129;                            // floats per staged row
 constexpr int kStagingBytes = 32 * kStagingStride * 4;         // per epilogue warp
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStagesTc; ++i) {
             mbar_init(full_a + 8 * i, 1);
-            mbar_init(full_b + 8 * i, kDecodeWarps);
+            mbar_init(full_b + 8 * i, kDecodeWarps / 2);
             mbar_init(empty + 8 * i, 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -225,36 +226,49 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
         }
     } else {
         // ---- decoders: trellis tiles -> swizzled K-major B stage -------------------------------
-        const int d = warp - (2 + kEpiWarps);  // column tile of the 128-column block
+        const int d = (warp - (2 + kEpiWarps)) & 7;   // column tile of the 128-column block
+        const int grp = (warp - (2 + kEpiWarps)) >> 3;  // this group owns iterations it = grp, grp+2, ...
         const LaneGeom<K> geom(lane);
         const int n0 = d * 16 + (lane >> 2), kq = 2 * (lane & 3);
-        long long it = 0;
-        for (long long t = blockIdx.x; t < tiles && !s_abort; t += gridDim.x) {
-            const int nb = (int)(t / args.m_pairs);
-            const uint32_t* column = c.w.packed + (((size_t)nb * ktiles16) * 8 + d) * (8 * K);
-            for (int ks = 0; ks < kt64; ++ks, ++it) {
-                const int st = (int)(it % kStagesTc);
-                if (it >= kStagesTc &&
-                    !mbar_wait(empty + 8 * st, (uint32_t)((it / kStagesTc) - 1) & 1, c.status, kTimeoutTensorPipe)) {
-                    s_abort = 1;
-                    break;
-                }
-                unsigned char* bt = ring + (size_t)st * kStageBytesTc + kMT * kTileBytes;
+        const long long my_tiles = tiles > blockIdx.x ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const long long iters = my_tiles * kt64;
+        // ring words of the four k-tiles of iteration `it` (tile = it / kt64 of this CTA, K step = it % kt64)
+        auto fetch = [&](long long it, uint32_t (&w)[4][3]) {
+            const long long t = blockIdx.x + (it / kt64) * gridDim.x;
+            const int nb = (int)(t / args.m_pairs), ks = (int)(it % kt64);
+            const uint32_t* tile = c.w.packed + ((((size_t)nb * ktiles16) + (size_t)ks * 4) * 8 + d) * (8 * K);
 #pragma unroll
-                for (int k4 = 0; k4 < 4; ++k4) {
-                    uint32_t frag[4];
-                    decode_tile_frag<K, CB>(column + (size_t)(ks * 4 + k4) * 8 * (8 * K), geom, frag);
-                    const int k = k4 * 16 + kq;
-                    // frag[0]: (n0, k..k+1)  frag[2]: (n0, k+8..)  frag[1]: (n0+8, k..)  frag[3]: (n0+8, k+8..)
-                    *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0, k)) = frag[0];
-                    *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0, k + 8)) = frag[2];
-                    *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0 + 8, k)) = frag[1];
-                    *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0 + 8, k + 8)) = frag[3];
-                }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full_b + 8 * st);
+            for (int k4 = 0; k4 < 4; ++k4) load_window<K>(tile + (size_t)k4 * 8 * (8 * K), geom, w[k4]);
+        };
+        uint32_t cur[4][3], nxt[4][3];
+        if (grp < iters) fetch(grp, cur);
+        for (long long it = grp; it < iters && !s_abort; it += 2) {
+            const int st = (int)(it % kStagesTc);
+            if (it + 2 < iters) fetch(it + 2, nxt);  // in flight while this stage is decoded
+            if (it >= kStagesTc &&
+                !mbar_wait(empty + 8 * st, (uint32_t)((it / kStagesTc) - 1) & 1, c.status, kTimeoutTensorPipe)) {
+                s_abort = 1;
+                break;
             }
+            unsigned char* bt = ring + (size_t)st * kStageBytesTc + kMT * kTileBytes;
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+                uint32_t frag[4];
+                decode_words_frag<K, CB>(cur[k4], geom, frag);
+                const int k = k4 * 16 + kq;
+                // frag[0]: (n0, k..k+1)  frag[2]: (n0, k+8..)  frag[1]: (n0+8, k..)  frag[3]: (n0+8, k+8..)
+                *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0, k)) = frag[0];
+                *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0, k + 8)) = frag[2];
+                *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0 + 8, k)) = frag[1];
+                *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0 + 8, k + 8)) = frag[3];
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_b + 8 * st);
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4)
+#pragma unroll
+                for (int j = 0; j < 3; ++j) cur[k4][j] = nxt[k4][j];
         }
     }
 

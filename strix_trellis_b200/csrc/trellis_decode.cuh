@@ -183,6 +183,17 @@ __device__ __forceinline__ void decode_tile_frag(const uint32_t* tile, const Lan
     frag[3] = codebook_pair<CB>(s[6], s[7]);
 }
 
+// The same from ring words that are already in registers (software-pipelined callers).
+template <int K, int CB>
+__device__ __forceinline__ void decode_words_frag(const uint32_t (&w)[3], const LaneGeom<K>& g, uint32_t (&frag)[4]) {
+    uint32_t s[8];
+    extract_states<K>(w, g, s);
+    frag[0] = codebook_pair<CB>(s[0], s[1]);
+    frag[2] = codebook_pair<CB>(s[2], s[3]);
+    frag[1] = codebook_pair<CB>(s[4], s[5]);
+    frag[3] = codebook_pair<CB>(s[6], s[7]);
+}
+
 template <int K, int CB>
 __device__ __forceinline__ void decode_tile_frag(const uint32_t* tile, int lane, uint32_t (&frag)[4]) {
     const LaneGeom<K> g(lane);
