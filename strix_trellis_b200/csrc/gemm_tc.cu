@@ -7,15 +7,15 @@
 //
 // Two launches: (1) input stages, writing the RN16 core input as pre-swizzled
 // [128 rows x 64 k] tiles so that each tile is ONE contiguous 16 KB bulk copy;
-// (2) the persistent GEMM kernel, one CTA per SM, CTA tile = 256 rows x 128 columns
-// (two 128-row accumulators share every decoded weight stage), K stepped by 64.
+// (2) the persistent GEMM kernel, one CTA per SM.  CTA tile = 256 rows x 256 columns as
+// 2 x (128 x 256) accumulators = all 512 TMEM columns: every decoded weight stage feeds
+// 256 rows and every activation tile feeds 256 columns.  K is stepped by 64.
 //   warp 0      A producer  : cp.async.bulk of the two A tiles of a stage
 //   warp 1      MMA issuer  : tcgen05.mma (one thread), tcgen05.commit to the barriers
 //   warps 2-5   epilogue    : tcgen05.ld -> shared staging -> H128 by warp shuffles -> y
-//   warps 6-21  decoders    : trellis tiles -> B stage in shared memory; two groups of
-//                             eight take alternate stages, next stage's words prefetched
-// TMEM: 2 tile buffers x (2 x 128) columns, so the epilogue of one tile overlaps the
-// main loop of the next.  Every wait is bounded.
+//   warps 6-21  decoders    : one warp per 16-column tile, 4 k-tiles per stage, the next
+//                             stage's ring words prefetched into registers
+// Every wait is bounded and reports into the device status word.
 #include <cstdlib>
 
 #include "backend.h"
@@ -27,21 +27,25 @@
 namespace st {
 
 namespace {
-constexpr int kBM = 128, kMT = 2, kBN = 128, kBK = 64;
+constexpr int kBM = 128, kMT = 2, kBN = 256, kBK = 64;
 constexpr int kStagesTc = 3;
-constexpr int kTileBytes = kBM * kBK * 2;                      // 16 KB
-constexpr int kStageBytesTc = (kMT + 1) * kTileBytes;          // A0, A1, B
-constexpr int kDecodeWarps = 16, kEpiWarps = 4;  // two decode groups leapfrog over the stages
+constexpr int kTileBytes = kBM * kBK * 2;                      // 16 KB: 128 rows x 64 binary16
+constexpr int kStageBytesTc = (kMT + kBN / 128) * kTileBytes;  // A0, A1, B (256 rows)
+constexpr int kDecodeWarps = 16, kEpiWarps = 4;                // one decode warp per column tile
 constexpr int kThreadsTc = (2 + kEpiWarps + kDecodeWarps) * 32;
 constexpr int kStagingStride = 129;                            // floats per staged row
-constexpr int kStagingBytes = 32 * kStagingStride * 4;         // per epilogue warp
-constexpr size_t kSmemTc = 1024 + (size_t)kStagesTc * kStageBytesTc + (size_t)kEpiWarps * kStagingBytes + 256;
+constexpr int kStagingBytes = 16 * kStagingStride * 4;         // per epilogue warp, 16 rows at a time
+constexpr size_t kSmemTc = 1024 + (size_t)kStagesTc * kStageBytesTc + (size_t)kEpiWarps * kStagingBytes + 128;
 constexpr uint32_t kTmemCols = 512;
 
 struct GemmArgs {
     LinearCall call;
     const unsigned char* a_tiles;  // [M/128 padded][I/64][16 KB]
     int m_pairs;                   // ceil(rows / 256)
+    int n_pairs;                   // ceil(column blocks / 2)
+#ifdef ST_DEBUG
+    int debug_mode;
+#endif
 };
 }  // namespace
 
@@ -82,7 +86,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kt64 = c.w.inputs / 64, ktiles16 = c.w.inputs / 16;
     const int nblocks = c.w.outputs / 128;
-    const long long tiles = (long long)nblocks * args.m_pairs;
+    // tiles ordered with the row pair fastest: CTAs that run together share a weight stripe
+    const int tiles = args.n_pairs * args.m_pairs;
+    const int my_tiles = tiles > (int)blockIdx.x ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
 
     unsigned char* ring = smem;
     float* staging = reinterpret_cast<float*>(ring + (size_t)kStagesTc * kStageBytesTc);
@@ -92,18 +98,16 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
     __shared__ int s_abort;
     const uint32_t full_a = smem_u32(bars), full_b = smem_u32(bars + kStagesTc),
                    empty = smem_u32(bars + 2 * kStagesTc), tmem_full = smem_u32(bars + 3 * kStagesTc),
-                   tmem_empty = smem_u32(bars + 3 * kStagesTc + 2);
+                   tmem_empty = smem_u32(bars + 3 * kStagesTc + 1);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStagesTc; ++i) {
             mbar_init(full_a + 8 * i, 1);
-            mbar_init(full_b + 8 * i, kDecodeWarps / 2);
+            mbar_init(full_b + 8 * i, kDecodeWarps);
             mbar_init(empty + 8 * i, 1);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(tmem_full + 8 * i, 1);
-            mbar_init(tmem_empty + 8 * i, kEpiWarps);
-        }
+        mbar_init(tmem_full, 1);
+        mbar_init(tmem_empty, kEpiWarps);
         mbar_fence_init();
         s_abort = 0;
     }
@@ -116,11 +120,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
     if (warp == 0) {
         // ---- A producer ---------------------------------------------------------------
         if (lane == 0) {
-            long long it = 0;
-            for (long long t = blockIdx.x; t < tiles && !s_abort; t += gridDim.x) {
-                const int mp = (int)(t % args.m_pairs);
+            int it = 0;
+            for (int lt = 0; lt < my_tiles && !s_abort; ++lt) {
+                const int t = (int)blockIdx.x + lt * (int)gridDim.x;
+                const int mp = t % args.m_pairs;
                 for (int ks = 0; ks < kt64; ++ks, ++it) {
-                    const int st = (int)(it % kStagesTc);
+                    const int st = it % kStagesTc;
                     if (it >= kStagesTc &&
                         !mbar_wait(empty + 8 * st, (uint32_t)((it / kStagesTc) - 1) & 1, c.status, kTimeoutTensorPipe)) {
                         s_abort = 1;
@@ -136,25 +141,22 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                 }
             }
             // Never leave with a copy still landing in this CTA's shared memory.
-            for (long long i = (it > kStagesTc ? it - kStagesTc : 0); i < it; ++i)
-                mbar_wait(full_a + 8 * (int)(i % kStagesTc), (uint32_t)(i / kStagesTc) & 1, c.status, kTimeoutDrain);
+            for (int i = (it > kStagesTc ? it - kStagesTc : 0); i < it; ++i)
+                mbar_wait(full_a + 8 * (i % kStagesTc), (uint32_t)(i / kStagesTc) & 1, c.status, kTimeoutDrain);
         }
     } else if (warp == 1) {
         // ---- MMA issuer ---------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_f16_f32(kBM, kBN);
-            long long it = 0;
-            int local_tile = 0;
-            for (long long t = blockIdx.x; t < tiles && !s_abort; t += gridDim.x, ++local_tile) {
-                const int buf = local_tile & 1;
-                if (local_tile >= 2 &&
-                    !mbar_wait(tmem_empty + 8 * buf, (uint32_t)((local_tile >> 1) - 1) & 1, c.status, kTimeoutTensorPipe)) {
+            int it = 0;
+            for (int lt = 0; lt < my_tiles && !s_abort; ++lt) {
+                if (lt >= 1 && !mbar_wait(tmem_empty, (uint32_t)(lt - 1) & 1, c.status, kTimeoutTensorPipe)) {
                     s_abort = 1;
                     break;
                 }
                 tc_fence_after_sync();
                 for (int ks = 0; ks < kt64 && !s_abort; ++ks, ++it) {
-                    const int st = (int)(it % kStagesTc);
+                    const int st = it % kStagesTc;
                     const uint32_t par = (uint32_t)(it / kStagesTc) & 1;
                     if (!mbar_wait(full_a + 8 * st, par, c.status, kTimeoutTensorPipe) ||
                         !mbar_wait(full_b + 8 * st, par, c.status, kTimeoutTensorPipe)) {
@@ -169,98 +171,143 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                         const uint64_t adesc = umma_desc_k_major_sw128(base + mt * kTileBytes);
 #pragma unroll
                         for (int k4 = 0; k4 < kBK / 16; ++k4)  // +32 bytes per 16-element K step
-                            umma_f16(tmem_base + buf * (kMT * kBN) + mt * kBN, adesc + 2 * k4, bdesc + 2 * k4, idesc,
-                                     (ks | k4) != 0);
+                            umma_f16(tmem_base + mt * kBN, adesc + 2 * k4, bdesc + 2 * k4, idesc, (ks | k4) != 0);
                     }
                     umma_commit(empty + 8 * st);  // stage reusable once these MMAs have read it
                 }
-                umma_commit(tmem_full + 8 * buf);  // accumulators of this tile complete
+                umma_commit(tmem_full);  // accumulators of this tile complete
             }
         }
     } else if (warp < 2 + kEpiWarps) {
         // ---- epilogue -------------------------------------------------------------------
         const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. +31
-        float* stage = staging + (size_t)(warp - 2) * 32 * kStagingStride;
-        int local_tile = 0;
-        for (long long t = blockIdx.x; t < tiles; t += gridDim.x, ++local_tile) {
-            const int buf = local_tile & 1;
-            const int nb = (int)(t / args.m_pairs), mp = (int)(t % args.m_pairs);
-            if (s_abort || !mbar_wait(tmem_full + 8 * buf, (uint32_t)(local_tile >> 1) & 1, c.status, kTimeoutTensorPipe)) {
+        float* stage = staging + (size_t)(warp - 2) * 16 * kStagingStride;
+        for (int lt = 0; lt < my_tiles; ++lt) {
+            const int t = (int)blockIdx.x + lt * (int)gridDim.x;
+            const int np = t / args.m_pairs, mp = t % args.m_pairs;
+            if (s_abort || !mbar_wait(tmem_full, (uint32_t)lt & 1, c.status, kTimeoutTensorPipe)) {
                 s_abort = 1;
                 break;
             }
             tc_fence_after_sync();
             for (int mt = 0; mt < kMT; ++mt) {
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (kMT * kBN) + mt * kBN;
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(taddr + ch * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) stage[lane * kStagingStride + ch * 32 + j] = __uint_as_float(r[j]);
-                }
-                if (mt == kMT - 1) {  // both accumulators read: hand the TMEM buffer back
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tmem_empty + 8 * buf);
-                }
-                __syncwarp();
-                const int row_base = (mp * kMT + mt) * kBM + quarter * 32;
-                for (int r = 0; r < 32; ++r) {
-                    const int row = row_base + r;
-                    if (row >= c.rows) break;
-                    float v[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[j] = stage[r * kStagingStride + lane + 32 * j];
-                    hadamard128_warp(v, lane);
+                for (int cb = 0; cb < kBN / 128; ++cb) {
+                    const int nb = np * (kBN / 128) + cb;
+                    if (nb >= nblocks) continue;  // odd column-block count: second half is padding
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + mt * kBN + cb * 128;
+                    // per-column constants of this lane's four columns, loaded once per block
+                    float sv[4], bi[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int cidx = nb * 128 + lane + 32 * j;
-                        float* out = c.y + (long long)row * c.y_stride + cidx;
-                        *out = finish_output(v[j], c.w.svh[cidx], c.w.bias, cidx, c.alpha, c.beta, out);
+                        sv[j] = half_bits_to_float(c.w.svh[cidx]);
+                        bi[j] = c.w.bias ? c.w.bias[cidx] : 0.f;
+                    }
+                    for (int half = 0; half < 2; ++half) {  // lanes [16*half, +16) stage their rows
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {
+                            uint32_t r[32];
+                            tmem_ld_32x32(taddr + ch * 32, r);
+                            tmem_ld_wait();
+                            if ((lane >> 4) == half) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    stage[(lane & 15) * kStagingStride + ch * 32 + j] = __uint_as_float(r[j]);
+                            }
+                        }
+                        __syncwarp();
+                        const int row_base = (mp * kMT + mt) * kBM + quarter * 32 + half * 16;
+#ifdef ST_DEBUG
+                        if (!(args.debug_mode & 2))
+#endif
+                        for (int r4 = 0; r4 < 16; r4 += 4) {  // four independent rows in flight
+                            float v[4][4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) v[u][j] = stage[(r4 + u) * kStagingStride + lane + 32 * j];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) hadamard128_warp(v[u], lane);
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const int row = row_base + r4 + u;
+                                if (row < c.rows) {
+                                    float* out = c.y + (long long)row * c.y_stride + nb * 128 + lane;
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        float value = __fmul_rn(v[u][j], sv[j]);
+                                        if (c.w.bias) value = __fadd_rn(value, bi[j]);
+                                        value = __fmul_rn(value, c.alpha);
+                                        if (c.beta != 0.0f) value = __fadd_rn(value, __fmul_rn(c.beta, out[32 * j]));
+                                        out[32 * j] = value;
+                                    }
+                                }
+                            }
+                        }
+                        __syncwarp();
                     }
                 }
-                __syncwarp();
             }
+            // all four accumulators read: hand tensor memory back to the MMA warp
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty);
         }
     } else {
         // ---- decoders: trellis tiles -> swizzled K-major B stage -------------------------------
-        const int d = (warp - (2 + kEpiWarps)) & 7;   // column tile of the 128-column block
-        const int grp = (warp - (2 + kEpiWarps)) >> 3;  // this group owns iterations it = grp, grp+2, ...
+        const int d = warp - (2 + kEpiWarps);  // column tile 0..15 of the 256-column stripe
+        const int cb = d >> 3, ct = d & 7;
         const LaneGeom<K> geom(lane);
         const int n0 = d * 16 + (lane >> 2), kq = 2 * (lane & 3);
-        const long long my_tiles = tiles > blockIdx.x ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-        const long long iters = my_tiles * kt64;
-        // ring words of the four k-tiles of iteration `it` (tile = it / kt64 of this CTA, K step = it % kt64)
-        auto fetch = [&](long long it, uint32_t (&w)[4][3]) {
-            const long long t = blockIdx.x + (it / kt64) * gridDim.x;
-            const int nb = (int)(t / args.m_pairs), ks = (int)(it % kt64);
-            const uint32_t* tile = c.w.packed + ((((size_t)nb * ktiles16) + (size_t)ks * 4) * 8 + d) * (8 * K);
+        const uint32_t o00 = sw128_offset(n0, kq), o01 = sw128_offset(n0, kq + 8);
+        const uint32_t o10 = sw128_offset(n0 + 8, kq), o11 = sw128_offset(n0 + 8, kq + 8);
+        const int iters = my_tiles * kt64;
+        // (tile, K step) whose ring words are fetched next; advanced without divisions
+        int flt = 0, fks = 0, fetched = 0;
+        const uint32_t* fcol = nullptr;
+        bool fvalid = false;
+        auto fetch = [&](uint32_t (&w)[4][3]) {
+            if (fks == kt64) { fks = 0; ++flt; fcol = nullptr; }
+            if (!fcol) {
+                const int t = (int)blockIdx.x + flt * (int)gridDim.x;
+                const int nb = (t / args.m_pairs) * (kBN / 128) + cb;
+                fvalid = nb < nblocks;  // a padding stripe decodes nothing
+                fcol = c.w.packed + (((size_t)(fvalid ? nb : 0) * ktiles16) * 8 + ct) * (8 * K);
+            }
+            const uint32_t* tile = fcol + (size_t)fks * 4 * 8 * (8 * K);
+            if (fvalid) {
 #pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) load_window<K>(tile + (size_t)k4 * 8 * (8 * K), geom, w[k4]);
+                for (int k4 = 0; k4 < 4; ++k4) load_window<K>(tile + (size_t)k4 * 8 * (8 * K), geom, w[k4]);
+            }
+            ++fks;
+            ++fetched;
         };
-        uint32_t cur[4][3], nxt[4][3];
-        if (grp < iters) fetch(grp, cur);
-        for (long long it = grp; it < iters && !s_abort; it += 2) {
-            const int st = (int)(it % kStagesTc);
-            if (it + 2 < iters) fetch(it + 2, nxt);  // in flight while this stage is decoded
+        uint32_t cur[4][3] = {}, nxt[4][3] = {};
+        if (iters > 0) fetch(cur);
+        for (int it = 0; it < iters && !s_abort; ++it) {
+            const int st = it % kStagesTc;
+            if (fetched < iters) fetch(nxt);  // in flight while this stage is decoded
             if (it >= kStagesTc &&
                 !mbar_wait(empty + 8 * st, (uint32_t)((it / kStagesTc) - 1) & 1, c.status, kTimeoutTensorPipe)) {
                 s_abort = 1;
                 break;
             }
             unsigned char* bt = ring + (size_t)st * kStageBytesTc + kMT * kTileBytes;
+#ifdef ST_DEBUG
+            if (!(args.debug_mode & 1))
+#endif
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {
                 uint32_t frag[4];
                 decode_words_frag<K, CB>(cur[k4], geom, frag);
-                const int k = k4 * 16 + kq;
+                // a K step of 16 elements is two 16-byte chunks: the swizzle XORs the chunk index
+                // with the row, so stepping k4 toggles bits 5..6 of the byte offset
+                const uint32_t kx = (uint32_t)(k4 * 2) << 4;
                 // frag[0]: (n0, k..k+1)  frag[2]: (n0, k+8..)  frag[1]: (n0+8, k..)  frag[3]: (n0+8, k+8..)
-                *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0, k)) = frag[0];
-                *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0, k + 8)) = frag[2];
-                *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0 + 8, k)) = frag[1];
-                *reinterpret_cast<uint32_t*>(bt + sw128_offset(n0 + 8, k + 8)) = frag[3];
+                *reinterpret_cast<uint32_t*>(bt + (o00 ^ kx)) = frag[0];
+                *reinterpret_cast<uint32_t*>(bt + (o01 ^ kx)) = frag[2];
+                *reinterpret_cast<uint32_t*>(bt + (o10 ^ kx)) = frag[1];
+                *reinterpret_cast<uint32_t*>(bt + (o11 ^ kx)) = frag[3];
             }
             fence_async_smem();
             __syncwarp();
@@ -353,7 +400,12 @@ cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* work
     args.call = call;
     args.a_tiles = static_cast<const unsigned char*>(workspace);
     args.m_pairs = m_pairs;
-    const long long tiles = (long long)(call.w.outputs / 128) * m_pairs;
+    args.n_pairs = (call.w.outputs / 128 + kBN / 128 - 1) / (kBN / 128);
+#ifdef ST_DEBUG
+    if (const char* e = getenv("STRIX_DBG")) args.debug_mode = atoi(e);
+#endif
+    const long long tiles = (long long)args.n_pairs * m_pairs;
+    if (tiles > 0x3FFFFFFF) return cudaErrorInvalidValue;
     const int grid = (int)(tiles < plan.sm_count ? tiles : plan.sm_count);
     switch (call.w.codebook) {
     case CB_3INST: return launch_tc_bits<CB_3INST>(args, grid, stream);
