@@ -1,0 +1,336 @@
+// Grouped fused linears (see grouped.h).  One CTA = (problem, 128-column block, K
+// partition): a producer warp streams the contiguous weight bytes of that partition through
+// a shared-memory ring (1-D bulk copies), eight decode warps each own a 16-column tile and
+// feed mma.sync.m16n8k16; partial planes go to the problem's scratch and the last CTA of a
+// column block to arrive folds them in ascending K order and applies the output stages.
+// Same arithmetic per row as the single-layer GEMV; only the work split differs.  Replaces
+// the reference's per-expert projection kernels (src/tp_moe.hip:60-164,
+// src/tp_fused_device.hpp:19-126) and its grouped strided GEMV (src/dense_r1_group*.hip).
+#include "grouped.h"
+#include "hadamard.cuh"
+#include "sync_primitives.cuh"
+#include "trellis_decode.cuh"
+
+namespace st {
+
+namespace {
+constexpr int kWarps = 8;
+constexpr int kThreadsG = (kWarps + 1) * 32;
+constexpr int kMaxStages = 16;
+
+struct GroupedArgs {
+    const GroupedProblem* problems;
+    int ctas_per_problem;
+    int splits;
+    int stages;
+    int hblocks;
+    int stage_stride;  // bytes between ring slots (sized for the largest rate in the group)
+    unsigned int* status;
+};
+
+// Decode loop of one CTA for rate K.  Returns false when a bounded wait gave up.
+template <int K, int CB>
+__device__ __forceinline__ bool consume(const unsigned char* ring, int stage_stride, int stages, int nblk, uint32_t full0,
+                                        uint32_t empty0, const uint2* act_lane, int rows, int warp, int lane,
+                                        unsigned int* status, float (&acc)[2][4]) {
+    const LaneGeom<K> geom(lane);
+    for (int i = 0; i < nblk; ++i) {
+        const int st = i % stages;
+        if (!mbar_wait(full0 + 8 * st, (uint32_t)(i / stages) & 1, status, kTimeoutRingFull)) return false;
+        const uint32_t* tiles = reinterpret_cast<const uint32_t*>(ring + (size_t)st * stage_stride) + warp * (8 * K);
+        const uint2* bsrc = act_lane + (size_t)i * rows * 32;
+#pragma unroll
+        for (int kt = 0; kt < 8; kt += 2) {
+            uint32_t fa[4], fb[4];
+            decode_tile_frag<K, CB>(tiles + kt * 8 * (8 * K), geom, fa);
+            decode_tile_frag<K, CB>(tiles + (kt + 1) * 8 * (8 * K), geom, fb);
+            const uint2 ba = bsrc[kt * 4], bb = bsrc[(kt + 1) * 4];
+            mma_16816(acc[0], fa, ba.x, ba.y);
+            mma_16816(acc[1], fb, bb.x, bb.y);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * st);
+    }
+    return true;
+}
+}  // namespace
+
+template <int CB>
+__global__ void __launch_bounds__(kThreadsG, 2) grouped_linear_kernel(const GroupedArgs args) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int pidx = blockIdx.x / args.ctas_per_problem, rem = blockIdx.x % args.ctas_per_problem;
+    const GroupedProblem& pr = args.problems[pidx];
+    // problem tables may have been written by the prior grid (device routing)
+    pdl_wait_prior_grid();
+    const int rows = pr.rows;
+    if (rows == 0) return;
+    const DeviceWeights w = pr.w;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = rem / args.splits, split = rem % args.splits;
+    const int hblocks = args.hblocks;
+    const int hb_begin = (int)((long long)hblocks * split / args.splits);
+    const int hb_end = (int)((long long)hblocks * (split + 1) / args.splits);
+    const int nblk = hb_end - hb_begin;
+    const int stages = args.stages;
+    const int stage_bytes = 2048 * w.bits;
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+    unsigned char* ring = smem + 256;
+    uint2* act = reinterpret_cast<uint2*>(ring + (size_t)stages * args.stage_stride);
+    __shared__ int s_last, s_abort;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kMaxStages);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < stages; ++i) {
+            mbar_init(full0 + 8 * i, 1);
+            mbar_init(empty0 + 8 * i, kWarps);
+        }
+        mbar_fence_init();
+        s_abort = 0;
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == kWarps) {
+        if (lane == 0) {
+            const unsigned char* stream = reinterpret_cast<const unsigned char*>(w.packed) +
+                ((size_t)nb * hblocks + hb_begin) * stage_bytes;
+            int issued = 0;
+            for (int i = 0; i < nblk; ++i) {
+                const int st = i % stages;
+                if (i >= stages && !mbar_wait(empty0 + 8 * st, (uint32_t)((i / stages) - 1) & 1, args.status, kTimeoutRingEmpty)) {
+                    s_abort = 1;
+                    break;
+                }
+                mbar_expect_tx(full0 + 8 * st, stage_bytes);
+                bulk_load(smem_u32(ring + (size_t)st * args.stage_stride), stream + (size_t)i * stage_bytes, stage_bytes,
+                          full0 + 8 * st);
+                issued = i + 1;
+            }
+            for (int i = (issued > stages ? issued - stages : 0); i < issued; ++i)
+                mbar_wait(full0 + 8 * (i % stages), (uint32_t)(i / stages) & 1, args.status, kTimeoutDrain);
+        }
+    } else {
+        // input stages of the gathered rows for this K partition, in B-fragment order
+        __half* act_h = reinterpret_cast<__half*>(act);
+        for (int item = warp; item < rows * nblk; item += kWarps) {
+            const int r = item / nblk, blk = item % nblk;
+            const float* xr = pr.x + (long long)pr.x_row[r] * pr.x_stride + (size_t)(hb_begin + blk) * 128;
+            const uint16_t* su = w.suh + (size_t)(hb_begin + blk) * 128;
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = __half2float(scale_input(xr[lane + 32 * j], su[lane + 32 * j]));
+            hadamard128_warp(v, lane);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int e = lane + 32 * j, kt = e >> 4, kk = e & 15;
+                const int q = (kk & 7) >> 1, hi = kk >> 3, lo = kk & 1;
+                act_h[((((size_t)blk * rows + r) * 8 + kt) * 4 + q) * 4 + hi * 2 + lo] = __float2half_rn(v[j]);
+            }
+        }
+        named_barrier(1, kWarps * 32);
+
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        const int brow = (lane >> 2) < rows ? (lane >> 2) : rows - 1;
+        const uint2* act_lane = act + brow * 32 + (lane & 3);
+        bool ok;
+        switch (w.bits) {
+        case 1: ok = consume<1, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
+        case 2: ok = consume<2, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
+        case 3: ok = consume<3, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
+        case 4: ok = consume<4, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
+        case 5: ok = consume<5, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
+        case 6: ok = consume<6, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
+        case 7: ok = consume<7, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
+        default: ok = consume<8, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
+        }
+        if (!ok) s_abort = 1;
+        const int col = warp * 16 + (lane >> 2), r0 = 2 * (lane & 3);
+        float* p = pr.partials + (((size_t)nb * args.splits + split) * rows) * 128;
+        const float v00 = acc[0][0] + acc[1][0], v01 = acc[0][1] + acc[1][1];
+        const float v10 = acc[0][2] + acc[1][2], v11 = acc[0][3] + acc[1][3];
+        if (r0 < rows) { p[r0 * 128 + col] = v00; p[r0 * 128 + col + 8] = v10; }
+        if (r0 + 1 < rows) { p[(r0 + 1) * 128 + col] = v01; p[(r0 + 1) * 128 + col + 8] = v11; }
+        __threadfence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int seen = atomicAdd(&pr.counters[nb], 1u);
+        const int last = (seen == (unsigned int)args.splits - 1);
+        if (last) { pr.counters[nb] = 0; __threadfence(); }
+        s_last = last && !s_abort;
+    }
+    __syncthreads();
+    if (!s_last || warp >= rows) return;
+    {
+        const int r = warp;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < args.splits; ++s) {
+            const float* p = pr.partials + (((size_t)nb * args.splits + s) * rows + r) * 128;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = __fadd_rn(v[j], __ldcg(p + lane + 32 * j));
+        }
+        hadamard128_warp(v, lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int cidx = nb * 128 + lane + 32 * j;
+            float* out = pr.y + (long long)pr.y_row[r] * pr.y_stride + cidx;
+            *out = finish_output(v[j], w.svh[cidx], w.bias, cidx, 1.0f, 0.0f, out);
+        }
+    }
+}
+
+GroupedPlan plan_grouped(int inputs, int outputs, int max_bits, int problems, int sm_count) {
+    GroupedPlan plan{};
+    const int hblocks = inputs / 128, nblocks = outputs / 128;
+    const int cap = 32;  // H128 blocks of K per CTA: 8 rows x 32 blocks x 256 B = 64 KB of core input
+    int splits = (hblocks + cap - 1) / cap;
+    // enough CTAs for two per SM across the whole group, but no more partitions than blocks
+    while ((long long)problems * nblocks * splits < 2LL * sm_count && splits * 2 <= hblocks && splits < 16) splits *= 2;
+    const int per = (hblocks + splits - 1) / splits;
+    int stages = (32 * 1024) / (2048 * max_bits);
+    if (stages > per) stages = per;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 1) stages = 1;
+    plan.splits = splits;
+    plan.stages = stages;
+    plan.ctas_per_problem = nblocks * splits;
+    plan.stage_stride = 2048 * max_bits;
+    plan.smem_bytes = 256 + (size_t)stages * plan.stage_stride + (size_t)per * 256 * kGroupRows;
+    plan.counter_bytes_per_problem = align_up((size_t)nblocks * sizeof(unsigned int));
+    plan.partial_bytes_per_problem = align_up((size_t)nblocks * splits * kGroupRows * 128 * sizeof(float));
+    return plan;
+}
+
+template <int CB>
+static cudaError_t launch_grouped_cb(const GroupedArgs& args, int grid, size_t smem, bool pdl, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(grouped_linear_kernel<CB>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(110 * 1024));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreadsG);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, grouped_linear_kernel<CB>, args);
+}
+
+cudaError_t launch_grouped(const GroupedProblem* problems, int problem_count, int inputs, int outputs,
+                           int codebook, const GroupedPlan& plan, unsigned int* status, bool programmatic,
+                           cudaStream_t stream) {
+    if (problem_count <= 0) return cudaSuccess;
+    (void)outputs;
+    GroupedArgs args{problems, plan.ctas_per_problem, plan.splits, plan.stages, inputs / 128, plan.stage_stride, status};
+    const long long grid = (long long)problem_count * plan.ctas_per_problem;
+    if (grid > 0x7FFFFFFF || plan.smem_bytes > 110 * 1024) return cudaErrorInvalidValue;
+    switch (codebook) {
+    case CB_3INST: return launch_grouped_cb<CB_3INST>(args, (int)grid, plan.smem_bytes, programmatic, stream);
+    case CB_MCG: return launch_grouped_cb<CB_MCG>(args, (int)grid, plan.smem_bytes, programmatic, stream);
+    case CB_MUL1: return launch_grouped_cb<CB_MUL1>(args, (int)grid, plan.smem_bytes, programmatic, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+// ---- SwiGLU and routed-expert combine --------------------------------------------------------
+__global__ void swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                              float* __restrict__ hidden, long long count, int width, long long out_stride) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
+         i += (long long)gridDim.x * blockDim.x) {
+        const float g = gate[i];
+        const float e = expf(g < 0.0f ? g : -g);  // stable sigmoid
+        const float d = __fadd_rn(1.0f, e);
+        const float sig = g < 0.0f ? __fdiv_rn(e, d) : __fdiv_rn(1.0f, d);
+        hidden[(i / width) * out_stride + (i % width)] = __fmul_rn(__fmul_rn(g, sig), up[i]);
+    }
+}
+
+cudaError_t launch_swiglu(const float* gate, const float* up, float* hidden, int rows, int width,
+                          long long out_stride, cudaStream_t stream) {
+    const long long count = (long long)rows * width;
+    if (count <= 0) return cudaSuccess;
+    const long long want = (count + 255) / 256;
+    swiglu_kernel<<<(int)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(gate, up, hidden, count, width, out_stride);
+    return cudaGetLastError();
+}
+
+// One thread per token: a row is valid when its ids are in range and distinct and its scores
+// are finite and non-negative (src/tp_moe_routes.hpp:46-61).  Slots of invalid rows run nothing.
+__global__ void moe_route_kernel(const unsigned int* __restrict__ ids, const float* __restrict__ scores,
+                                 int tokens, int top_k, const MoeBankEntry* __restrict__ bank, int bank_count,
+                                 GroupedProblem* gate_up, GroupedProblem* down, int* row_valid) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens) return;
+    bool valid = true;
+    for (int s = 0; s < top_k && valid; ++s) {
+        const unsigned int id = ids[t * top_k + s];
+        const float sc = scores[t * top_k + s];
+        if (id >= (unsigned int)bank_count || !(sc >= 0.0f && sc <= 3.402823466e+38f)) valid = false;
+        for (int q = 0; q < s && valid; ++q)
+            if (ids[t * top_k + q] == id) valid = false;
+    }
+    row_valid[t] = valid ? 1 : 0;
+    for (int s = 0; s < top_k; ++s) {
+        const int p = t * top_k + s;
+        const unsigned int id = valid ? ids[p] : 0u;
+        gate_up[2 * p].rows = gate_up[2 * p + 1].rows = valid ? 1 : 0;
+        down[p].rows = (valid && scores[p] != 0.0f) ? 1 : 0;
+        if (valid) {
+            gate_up[2 * p].w = bank[id].gate;
+            gate_up[2 * p + 1].w = bank[id].up;
+            down[p].w = bank[id].down;
+        }
+    }
+}
+
+cudaError_t launch_moe_route(const unsigned int* route_ids, const float* route_scores, int tokens, int top_k,
+                             const MoeBankEntry* bank, int bank_count, GroupedProblem* gate_up, GroupedProblem* down,
+                             int* row_valid, cudaStream_t stream) {
+    moe_route_kernel<<<(tokens + 63) / 64, 64, 0, stream>>>(route_ids, route_scores, tokens, top_k, bank, bank_count,
+                                                           gate_up, down, row_valid);
+    return cudaGetLastError();
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ each, const float* __restrict__ scores,
+                                   const int* __restrict__ row_valid, int tokens, int top_k, int outputs,
+                                   float* y, long long y_stride, float alpha, float beta) {
+    const long long total = (long long)tokens * outputs;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / outputs), n = (int)(i % outputs);
+        float* out = y + (long long)t * y_stride + n;
+        if (row_valid && !row_valid[t]) {
+            *out = __int_as_float(0x7fc00000);
+            continue;
+        }
+        float sum = 0.0f;
+        for (int s = 0; s < top_k; ++s) {  // ascending slot order from +0
+            const float score = scores[t * top_k + s];
+            if (score == 0.0f) continue;
+            sum = __fadd_rn(sum, __fmul_rn(score, each[((long long)t * top_k + s) * outputs + n]));
+        }
+        float value = __fmul_rn(alpha, sum);
+        if (beta != 0.0f) value = __fadd_rn(value, __fmul_rn(beta, *out));
+        *out = value;
+    }
+}
+
+cudaError_t launch_moe_combine(const float* each, const float* scores, const int* row_valid, int tokens,
+                               int top_k, int outputs, float* y, long long y_stride, float alpha, float beta,
+                               cudaStream_t stream) {
+    const long long total = (long long)tokens * outputs;
+    if (total <= 0) return cudaSuccess;
+    const long long want = (total + 255) / 256;
+    moe_combine_kernel<<<(int)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(
+        each, scores, row_valid, tokens, top_k, outputs, y, y_stride, alpha, beta);
+    return cudaGetLastError();
+}
+
+}  // namespace st

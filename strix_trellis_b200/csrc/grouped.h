@@ -1,0 +1,58 @@
+// Grouped linears: many independent complete linears of ONE geometry (inputs, outputs)
+// in one launch, each with its own weights (any rate 1..8), its own gathered input rows and
+// scattered output rows.  Building block of the routed-expert, SwiGLU and grouped-GEMV plans.
+#pragma once
+#include "backend.h"
+
+namespace st {
+
+constexpr int kGroupRows = 8;
+
+// One problem.  rows == 0 marks an unused slot (its CTAs exit at once).
+// Input row r is x + x_row[r]*x_stride, output row r is y + y_row[r]*y_stride.
+struct GroupedProblem {
+    DeviceWeights w;
+    const float* x;
+    float* y;
+    long long x_stride, y_stride;
+    int rows;
+    int x_row[kGroupRows];
+    int y_row[kGroupRows];
+    unsigned int* counters;  // [outputs/128], zero between launches
+    float* partials;         // [outputs/128][splits][rows][128]
+};
+
+struct GroupedPlan {
+    int splits;
+    int stages;
+    int ctas_per_problem;
+    int stage_stride;
+    size_t smem_bytes;
+    size_t counter_bytes_per_problem;
+    size_t partial_bytes_per_problem;  // for kGroupRows rows
+};
+GroupedPlan plan_grouped(int inputs, int outputs, int max_bits, int problems, int sm_count);
+// `problems` lives in device memory; slots with rows == 0 are skipped on the device.
+cudaError_t launch_grouped(const GroupedProblem* problems, int problem_count, int inputs, int outputs,
+                           int codebook, const GroupedPlan& plan, unsigned int* status, bool programmatic,
+                           cudaStream_t stream);
+
+// hidden[r][c] = SwiGLU(gate[r][c], up[r][c]); gate/up contiguous [rows][width], hidden rows
+// `out_stride` apart (src/tp_moe_activation.hpp:52-59).
+cudaError_t launch_swiglu(const float* gate, const float* up, float* hidden, int rows, int width,
+                          long long out_stride, cudaStream_t stream);
+
+// Device-side routing for a persistent expert bank: validates each token's route row and
+// fills the per-route problem slots (one row each) from the bank table.
+struct MoeBankEntry { DeviceWeights gate, up, down; };
+cudaError_t launch_moe_route(const unsigned int* route_ids, const float* route_scores, int tokens, int top_k,
+                             const MoeBankEntry* bank, int bank_count, GroupedProblem* gate_up, GroupedProblem* down,
+                             int* row_valid, cudaStream_t stream);
+
+// Routed-expert combine: y[t] = alpha * sum_{s ascending, from +0} RN32(score[t,s]*each[t,s]) + beta*y[t];
+// a zero score skips its slot; a row flagged invalid becomes NaN (src/tp_moe.hip:112-164).
+cudaError_t launch_moe_combine(const float* each, const float* scores, const int* row_valid, int tokens,
+                               int top_k, int outputs, float* y, long long y_stride, float alpha, float beta,
+                               cudaStream_t stream);
+
+}  // namespace st

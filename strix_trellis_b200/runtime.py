@@ -242,3 +242,70 @@ class LinearPlan:
         if self.handle:
             N.check(self.lib.strix_linear_plan_destroy(self.handle), "strix_linear_plan_destroy")
             self.handle = N.vp()
+
+
+class MoePlan:
+    """strix_tp_moe_plan over a list of experts [(gate, up, down) Weights].  With
+    `device_routed`, `route_ids` (uint32) and `route_scores` (float32) are CUDA tensors read
+    at every submit and `experts[i]` is bank entry i; otherwise they are host arrays frozen at
+    creation and `expert_ids[i]` names experts[i]."""
+
+    def __init__(self, ctx, experts, x, y, route_ids, route_scores, expert_ids=None, alpha=1.0, beta=0.0,
+                 device_routed=False, stream=None):
+        self.ctx, self.lib = ctx, ctx.lib
+        tokens = x.shape[0]
+        inter = experts[0][0].outputs
+        arr = (N.ExpertDesc * len(experts))()
+        for i, (g, u, d) in enumerate(experts):
+            arr[i].struct_size = C.sizeof(N.ExpertDesc)
+            arr[i].abi_version = N.ABI_VERSION
+            arr[i].expert_id = i if expert_ids is None else int(expert_ids[i])
+            arr[i].gate, arr[i].up, arr[i].down = g.handle, u.handle, d.handle
+        top_k = route_ids.numel() // tokens if device_routed else np.asarray(route_ids).size // tokens
+        self.workspace = torch.empty(max(tokens * top_k * inter * 4, 256), dtype=torch.uint8, device=x.device)
+        sd = _cur_stream(stream)
+        self.handle = N.vp()
+
+        def tensor(t):
+            nbytes = ((t.shape[0] - 1) * t.stride(0) + t.shape[1]) * 4
+            return N.tensor_desc(t.data_ptr(), nbytes, tuple(t.shape), (t.stride(0), t.stride(1)))
+
+        if device_routed:
+            d = N.MoeDeviceDesc()
+            self.lib.strix_tp_moe_device_desc_init(C.byref(d))
+            d.route_ids, d.route_ids_bytes = route_ids.data_ptr(), route_ids.numel() * 4
+            d.route_scores, d.route_scores_bytes = route_scores.data_ptr(), route_scores.numel() * 4
+            create = self.lib.strix_tp_moe_plan_create_device
+        else:
+            d = N.MoeDesc()
+            self.lib.strix_tp_moe_desc_init(C.byref(d))
+            ids = np.ascontiguousarray(route_ids, dtype=np.uint32)
+            sc = np.ascontiguousarray(route_scores, dtype=np.float32)
+            d.route_ids, d.route_ids_count = ids.ctypes.data, ids.size
+            d.route_scores, d.route_scores_count = sc.ctypes.data, sc.size
+            create = self.lib.strix_tp_moe_plan_create
+        d.input, d.output = tensor(x), tensor(y)
+        d.experts, d.expert_count = arr, len(experts)
+        d.workspace, d.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
+        d.alpha, d.beta = alpha, beta
+        self.keep = (x, y, arr, route_ids, route_scores)
+        N.check(create(ctx.handle, C.byref(d), C.byref(sd), C.byref(self.handle)), "strix_tp_moe_plan_create")
+        self.tokens, self.top_k, self.inter = tokens, top_k, inter
+
+    def submit(self):
+        N.check(self.lib.strix_tp_moe_plan_submit(self.handle), "strix_tp_moe_plan_submit")
+
+    def gate_up(self):
+        N.check(self.lib.strix_tp_moe_plan_gate_up(self.handle), "strix_tp_moe_plan_gate_up")
+
+    def down(self):
+        N.check(self.lib.strix_tp_moe_plan_down(self.handle), "strix_tp_moe_plan_down")
+
+    def hidden(self):
+        return self.workspace[: self.tokens * self.top_k * self.inter * 4].view(torch.float32).view(
+            self.tokens, self.top_k, self.inter)
+
+    def close(self):
+        if self.handle:
+            N.check(self.lib.strix_tp_moe_plan_destroy(self.handle), "strix_tp_moe_plan_destroy")
+            self.handle = N.vp()
