@@ -217,7 +217,7 @@ typedef struct strix_grouped_moe_desc {
 #define STRIX_TP_MAX_EXPERTS UINT32_C(48)
 #define STRIX_TP_MAX_BANK_EXPERTS UINT32_C(256)
 #define STRIX_B200_MOE_MAX_TOP_K UINT32_C(16)
-#define STRIX_B200_MOE_MAX_ROWS UINT32_C(64)
+#define STRIX_B200_MOE_MAX_ROWS UINT32_C(4096)
 #define STRIX_B200_MOE_MAX_BANK UINT32_C(1024)
 
 /* One routed expert: gate/up [N=inter, I=hidden], down [N=hidden, I=inter]. */

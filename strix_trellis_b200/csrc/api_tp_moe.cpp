@@ -589,7 +589,20 @@ strix_status strix_tp_swiglu_plan_create(strix_context c, const strix_tp_swiglu_
     if (s != STRIX_SUCCESS) return s;
     if (d->workspace_bytes < need) return STRIX_ERROR_INSUFFICIENT_BUFFER;
     if (!d->workspace || reinterpret_cast<uintptr_t>(d->workspace) % kAlign) return STRIX_ERROR_INVALID_ARGUMENT;
-    if (d->diagnostic_gate || d->diagnostic_up) return STRIX_ERROR_UNSUPPORTED_FORMAT;  // diagnostics not offered
+    // Optional diagnostics: the gate / up projections land in the caller's contiguous
+    // [rows, inter] buffers instead of the workspace.
+    const uint64_t diag_need = (uint64_t)rows * d->gate->device.outputs * 4;
+    for (float* diag : {d->diagnostic_gate, d->diagnostic_up}) {
+        if (!diag) continue;
+        if (d->diagnostic_bytes < diag_need) return STRIX_ERROR_INSUFFICIENT_BUFFER;
+        if (overlap(diag, diag_need, d->input.data, xb) || overlap(diag, diag_need, d->hidden_output.data, hb) ||
+            overlap(diag, diag_need, d->workspace, d->workspace_bytes))
+            return STRIX_ERROR_INVALID_ARGUMENT;
+        s = device_buffer(c, diag, diag_need, 4);
+        if (s != STRIX_SUCCESS) return s;
+    }
+    if (d->diagnostic_gate && d->diagnostic_up && overlap(d->diagnostic_gate, diag_need, d->diagnostic_up, diag_need))
+        return STRIX_ERROR_INVALID_ARGUMENT;
     if (overlap(d->input.data, xb, d->hidden_output.data, hb) || overlap(d->workspace, d->workspace_bytes, d->input.data, xb) ||
         overlap(d->workspace, d->workspace_bytes, d->hidden_output.data, hb))
         return STRIX_ERROR_INVALID_ARGUMENT;
@@ -607,6 +620,8 @@ strix_status strix_tp_swiglu_plan_create(strix_context c, const strix_tp_swiglu_
     p->g = carve.take<float>((size_t)rows * g.outputs);
     p->u = p->g + (size_t)rows * g.outputs;
     carve.used = st::align_up((size_t)2 * rows * g.outputs * 4);
+    if (d->diagnostic_gate) p->g = d->diagnostic_gate;
+    if (d->diagnostic_up) p->u = d->diagnostic_up;
     const size_t each = p->plan.counter_bytes_per_problem + p->plan.partial_bytes_per_problem;
     unsigned char* scratch = carve.take<unsigned char>(2 * each);
     p->problems = carve.take<st::GroupedProblem>(2);

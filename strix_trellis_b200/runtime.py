@@ -244,6 +244,28 @@ class LinearPlan:
             self.handle = N.vp()
 
 
+class DensePlan:
+    """strix_tp_dense_plan on F32 row views (unit channel stride, any row stride, rows 1..8);
+    scratch is the library's."""
+
+    def __init__(self, weights, x, y, alpha=1.0, beta=0.0, stream=None):
+        self.weights, self.lib = weights, weights.lib
+        d = weights.matmul_desc(x, y, alpha, beta)
+        sd = _cur_stream(stream)
+        self.handle = N.vp()
+        self.keep = (x, y)
+        N.check(self.lib.strix_tp_dense_plan_create(weights.ctx.handle, C.byref(d), C.byref(sd), C.byref(self.handle)),
+                "strix_tp_dense_plan_create")
+
+    def submit(self):
+        N.check(self.lib.strix_tp_dense_plan_submit(self.handle), "strix_tp_dense_plan_submit")
+
+    def close(self):
+        if self.handle:
+            N.check(self.lib.strix_tp_dense_plan_destroy(self.handle), "strix_tp_dense_plan_destroy")
+            self.handle = N.vp()
+
+
 class MoePlan:
     """strix_tp_moe_plan over a list of experts [(gate, up, down) Weights].  With
     `device_routed`, `route_ids` (uint32) and `route_scores` (float32) are CUDA tensors read
