@@ -6,8 +6,8 @@
 Workload (N=1): benchmark configuration 2 restricted to the rate and row count the
 metric names -- K=4 bits/weight, one activation row -- over its four shapes
 (4096x4096, 5120x5120, 1152x4096, 4096x14336), seeded synthetic weights.  A "step" is
-one pass over every weight clone of every shape; each shape has enough clones to
-exceed L2 four times over, so weights always come from HBM.  `value` is packed weight
+one launch of each of 24 device copies of each shape (96 launches, 1.28 GB of packed
+weights, ten times L2), so weights always come from HBM.  `value` is packed weight
 bytes per second (the reference's own definition, README.md:224-226) with inputs
 resident on the device and every call captured in one CUDA graph.  `e2e` is the same
 metric through the public C-ABI call (strix_linear_plan_submit) with HOST activations:
@@ -36,6 +36,7 @@ sys.path.insert(0, str(ROOT))
 
 SHAPES = [(4096, 4096), (5120, 5120), (1152, 4096), (4096, 14336)]
 BITS, ROWS = 4, 1
+CLONES = 24  # device copies per shape: 24 x (8.4 + 13.1 + 2.4 + 29.4) MB = 1.28 GB per step
 METRIC = "K4 R1 decode-GEMV GB/s over packed weight bytes"
 WORKLOAD = "config2: K4 R1 fused decode-GEMV sweep over (4096,4096),(5120,5120),(1152,4096),(4096,14336)"
 
@@ -132,6 +133,155 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def time_calls(torch, stream, fn, reps, warm=3):
+    """Average device time of fn() in microseconds: CUDA events on the launching stream."""
+    with torch.cuda.stream(stream):
+        for _ in range(warm):
+            fn()
+        stream.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(reps):
+            fn()
+        b.record(stream)
+        stream.synchronize()
+    return a.elapsed_time(b) * 1e3 / reps
+
+
+def gemm_case(torch, ctx, stream, rows_list, bits=4, inputs=4096, outputs=12288, reps=None):
+    """Prefill GEMM of benchmark configuration 3 (4096 -> 12288): microseconds and TFLOP/s."""
+    from strix_trellis_b200 import native as N, synthetic
+    w = ctx.prepare(synthetic.make_layer(inputs, outputs, bits, seed=synthetic.BASE_SEED + 300 + bits))
+    out = {}
+    for m in rows_list:
+        x = torch.from_numpy(synthetic.make_activations(m, inputs, seed=synthetic.BASE_SEED + 301)).cuda()
+        y = torch.empty((m, outputs), dtype=torch.float32, device="cuda")
+        ws = torch.empty(max(w.workspace_bytes(x, y), 256), dtype=torch.uint8, device="cuda")
+        with torch.cuda.stream(stream):
+            plan = w.plan(x, y, N.OP_GEMM, workspace=ws, stream=stream)
+        us = time_calls(torch, stream, plan.submit, reps or (10 if m <= 2048 else 4))
+        out[f"M{m}"] = {"us": round(us, 1), "TFLOPs": round(2.0 * m * inputs * outputs / us / 1e6, 1)}
+        plan.close()
+    w.close()
+    return out
+
+
+def moe_case(torch, ctx, stream, tokens_list, experts=32, top_k=8, model=4096, inter=2048, bits=2, reps=12):
+    """Routed-expert block of benchmark configuration 5 on one rank's bank of `experts`
+    experts (K2 gate/up/down, 201 MB of packed weights), device-routed.  Routes rotate over
+    four seeded sets between submits (one small device copy, inside the timed region) so that
+    successive submits read different experts.  Microseconds per submit."""
+    from strix_trellis_b200 import synthetic
+    from strix_trellis_b200.runtime import MoePlan
+    proto = [synthetic.make_layer(model, inter, bits, seed=synthetic.BASE_SEED + 500, sigma=0.5),
+             synthetic.make_layer(model, inter, bits, seed=synthetic.BASE_SEED + 501, sigma=0.5),
+             synthetic.make_layer(inter, model, bits, seed=synthetic.BASE_SEED + 502, sigma=0.5)]
+    bank = [tuple(ctx.prepare(l) for l in proto) for _ in range(experts)]  # distinct device copies
+    out = {}
+    for t in tokens_list:
+        x = torch.from_numpy(synthetic.make_activations(t, model, seed=synthetic.BASE_SEED + 503)).cuda()
+        y = torch.zeros((t, model), dtype=torch.float32, device="cuda")
+        sets = [synthetic.make_routes(t, experts, top_k, seed=synthetic.BASE_SEED + 504 + k) for k in range(4)]
+        ids_all = [torch.from_numpy(i.astype(np.uint32).view(np.int32)).cuda() for i, _ in sets]
+        sc_all = [torch.from_numpy(sc).cuda() for _, sc in sets]
+        ids_d, sc_d = ids_all[0].clone(), sc_all[0].clone()
+        with torch.cuda.stream(stream):
+            plan = MoePlan(ctx, bank, x, y, ids_d, sc_d, device_routed=True, stream=stream)
+        turn = [0]
+
+        def submit():
+            turn[0] = (turn[0] + 1) % 4
+            ids_d.copy_(ids_all[turn[0]])
+            sc_d.copy_(sc_all[turn[0]])
+            plan.submit()
+        us = time_calls(torch, stream, submit, reps)
+        routed = t * top_k * sum(l.packed_bytes for l in proto)
+        out[f"T{t}"] = {"us": round(us, 1), "GBps_over_routed_weight_bytes": round(routed / us / 1e3, 1)}
+        plan.close()
+    for e in bank:
+        for w in e:
+            w.close()
+    return out
+
+
+def tp_case(torch, dist, ctx, stream, rank, world, rows_list=(1, 4, 8), reps=24):
+    """Benchmark configuration 4 at `world` ranks: (a) row-parallel 16384 -> 4096 K5 with
+    all-reduce, (b) LM head 4096 -> 129280 K5 with all-gather.  Each rank generates only its
+    own shard and rotates over enough device copies of it to exceed L2 twice.  Microseconds
+    per call (local kernel + collective) and for the local kernel alone, max over ranks."""
+    from strix_trellis_b200 import synthetic, tp
+    from strix_trellis_b200.container import Exl3Tensor
+    from strix_trellis_b200.tp_runtime import ColumnParallelLinear, RowParallelLinear
+
+    def shard_layer(inputs, outputs, seed):
+        layer = synthetic.make_layer(inputs, outputs, 5, seed=seed + rank)
+        return Exl3Tensor(layer.trellis, layer.suh, layer.svh, 5.0, layer.codebook, None, "synthetic", "w"), layer
+
+    a0, a1 = tp.h128_bounds(16384, world)[rank]
+    b0, b1 = tp.h128_bounds(129280, world)[rank]
+    row_t, row_l = shard_layer(a1 - a0, 4096, synthetic.BASE_SEED + 600)
+    col_t, col_l = shard_layer(4096, b1 - b0, synthetic.BASE_SEED + 700)
+    need = 256 * 1024 * 1024
+    rows_ = [RowParallelLinear(ctx, row_t, rank, world, full_inputs=16384)
+             for _ in range(-(-need // row_l.packed_bytes))]
+    cols_ = [ColumnParallelLinear(ctx, col_t, rank, world, full_outputs=129280)
+             for _ in range(-(-need // col_l.packed_bytes))]
+    out = {"row_parallel_copies": len(rows_), "lm_head_copies": len(cols_)}
+    for r in rows_list:
+        x_row = torch.from_numpy(synthetic.make_activations(r, 16384, seed=synthetic.BASE_SEED + 601)).cuda()
+        y_row = torch.empty((r, 4096), dtype=torch.float32, device="cuda")
+        x_col = torch.from_numpy(synthetic.make_activations(r, 4096, seed=synthetic.BASE_SEED + 701)).cuda()
+        turn = [0]
+
+        def pick(pool):
+            turn[0] += 1
+            return pool[turn[0] % len(pool)]
+        wr, wc = max(3, len(rows_)), max(3, len(cols_))  # warm-up freezes every copy's plan
+        us = [time_calls(torch, stream, lambda: pick(rows_).forward(x_row, y_row), reps, wr),
+              time_calls(torch, stream, lambda: pick(rows_).local(x_row, y_row), reps, wr),
+              time_calls(torch, stream, lambda: pick(cols_).forward(x_col), reps, wc),
+              time_calls(torch, stream, lambda: pick(cols_).local(x_col), reps, wc)]
+        t = torch.tensor(us, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = [round(float(v), 1) for v in t.tolist()]
+        out[f"R{r}"] = {"row_parallel_us": us[0], "row_parallel_kernel_us": us[1],
+                        "lm_head_us": us[2], "lm_head_kernel_us": us[3]}
+    for layer in rows_ + cols_:
+        layer.close()
+    return out
+
+
+def run_case(args):
+    """A small fixed workload of one kernel, for profilers: a few launches, inputs larger
+    than L2, a few hundred MB on the device."""
+    import torch
+    from strix_trellis_b200 import native as N, synthetic
+    from strix_trellis_b200.runtime import Context
+    ctx = Context(0)
+    stream = torch.cuda.Stream()
+    if args.case == "gemv":
+        layer = synthetic.make_layer(4096, 14336, BITS, seed=synthetic.BASE_SEED + 3)
+        ws = [ctx.prepare(layer) for _ in range(8)]  # 8 x 29 MB: every launch reads cold weights
+        x = torch.from_numpy(synthetic.make_activations(ROWS, 4096)).cuda()
+        y = torch.empty((ROWS, 14336), dtype=torch.float32, device="cuda")
+        with torch.cuda.stream(stream):
+            plans = [w.plan(x, y, N.OP_GEMV, stream=stream) for w in ws]
+
+        def one_pass():
+            for p in plans:
+                p.submit()
+        us = time_calls(torch, stream, one_pass, 3, warm=1) / len(plans)
+        print(json.dumps({"case": "gemv 4096x14336 K4 R1", "us_per_launch": round(us, 2),
+                          "GBps": round(layer.packed_bytes / us / 1e3, 1), "status": ctx.device_status()}))
+    elif args.case == "gemm":
+        print(json.dumps({"case": "gemm 4096->12288 K4", **gemm_case(torch, ctx, stream, [2048], reps=2),
+                          "status": ctx.device_status()}))
+    else:
+        print(json.dumps({"case": "moe bank 32, top-8, 4096/2048 K2", **moe_case(torch, ctx, stream, [8], reps=2),
+                          "status": ctx.device_status()}))
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -146,12 +296,13 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ctx = Context(local)
 
-    # ---- weights: clones per shape so that each shape's rotation is >= 4x L2 ----------
-    rotation = 512 * 1024 * 1024
+    # ---- weights: the same number of device copies of every shape; one step launches each
+    # copy once, shape after shape, so a copy is read again only after the other 1.2 GB
+    # (ten times L2) went through ---------------------------------------------------------
+    clones = CLONES
     groups, total_bytes, launches = [], 0, 0
     for k, (inputs, outputs) in enumerate(SHAPES):
         layer = synthetic.make_layer(inputs, outputs, BITS, seed=synthetic.BASE_SEED + k)
-        clones = int(np.ceil(rotation / layer.packed_bytes))
         ws = [ctx.prepare(layer) for _ in range(clones)]
         x = torch.from_numpy(synthetic.make_activations(ROWS, inputs, seed=synthetic.BASE_SEED + 50 + k)).cuda()
         y = torch.empty((ROWS, outputs), dtype=torch.float32, device="cuda")
@@ -205,8 +356,10 @@ def run_gpu(args):
         while time.time() < t_end:
             graph.replay()
         stream.synchronize()
-    # per-shape launch time (own event pairs, same graph nodes' plans, stream launches)
+    # per-shape launch time: the shape's copies as one graph, L2 flushed (256 MB written)
+    # before each timed replay because the smallest shape's copies alone would fit in L2
     per_shape = {}
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     with torch.cuda.stream(stream):
         for g in groups:
             sub = torch.cuda.CUDAGraph()
@@ -215,17 +368,21 @@ def run_gpu(args):
                     p.submit()
             sub.replay()
             stream.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream)
+            total_ms = 0.0
             for _ in range(3):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
                 sub.replay()
-            b.record(stream)
-            stream.synchronize()
-            us = a.elapsed_time(b) * 1e3 / 3 / len(g["plans"])
+                b.record(stream)
+                stream.synchronize()
+                total_ms += a.elapsed_time(b)
+            us = total_ms * 1e3 / 3 / len(g["plans"])
             layer = g["layer"]
             per_shape[f"{layer.inputs}x{layer.outputs}"] = {
                 "us_per_launch": round(us, 3), "GBps": round(layer.packed_bytes / us / 1e3, 1)}
             del sub
+    del flush
     ms_t = torch.tensor([ms], device="cuda")
     if world > 1:
         dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
@@ -260,6 +417,29 @@ def run_gpu(args):
 
     clocks.__exit__()
     clock_summary = clocks.summary()
+
+    # ---- the other configurations of the metric, outside the timed region above ----------
+    for g in groups:  # free the clone rotations first
+        for p in g["plans"]:
+            p.close()
+        for w in g["weights"]:
+            w.close()
+    extra = {}
+    if not args.no_extra:
+        gemm_peak = 2250.0
+        if (ROOT / "MEASURED_PEAKS.json").exists():
+            gemm_peak = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"])
+        if rank == 0:
+            gemm = gemm_case(torch, ctx, stream, [128, 512, 2048, 8192])
+            for v in gemm.values():
+                v["frac_of_measured_dense_peak"] = round(v["TFLOPs"] / gemm_peak, 3)
+            extra["prefill_gemm_K4_4096x12288"] = gemm
+            extra["moe_bank32_top8_K2_one_rank"] = moe_case(torch, ctx, stream, [1, 8, 64])
+        if world > 1:
+            dist.barrier()
+        extra_tp = tp_case(torch, dist, ctx, stream, rank, world)
+        if rank == 0:
+            extra[f"tp_dense_K5_world{world}"] = extra_tp
     status = ctx.device_status()
     if status:
         raise SystemExit(f"device status word {status:#x}: a bounded wait gave up; numbers invalid")
@@ -279,7 +459,7 @@ def run_gpu(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16 weights, f32 accumulate", "data": "synthetic",
             "config": {"workload": WORKLOAD, "bits": BITS, "rows": ROWS,
-                       "cold_weights": "each shape rotates over >=512 MiB of weight clones (>4x L2)",
+                       "cold_weights": f"{CLONES} device copies per shape, each launched once per step: 1.28 GB (10x L2) between two reads of a copy",
                        "launches_per_step": launches, "parallelism": f"replicas x{world}",
                        "per_shape": per_shape},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
@@ -291,6 +471,7 @@ def run_gpu(args):
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": launches * args.steps,
             "clocks": clock_summary,
+            "extra": extra,
         }
         if base is not None:
             line["cpu_baseline"] = base
@@ -305,8 +486,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the GEMM / MoE / TP side measurements")
+    ap.add_argument("--case", choices=["gemv", "gemm", "moe"], help="run one small profiling workload and exit")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

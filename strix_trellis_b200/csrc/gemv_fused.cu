@@ -35,7 +35,15 @@ constexpr int kGroups = 2;                       // k-tile parities per column t
 constexpr int kConsumers = 8 * kGroups;          // decode warps
 constexpr int kThreads = (kConsumers + 2) * 32;  // + producer warp + epilogue warp
 constexpr int kDumpThreads = (kConsumers + 1) * 32;  // decode warps + epilogue warp
-constexpr int kActBytes = 32 * 1024;             // staged core input per CTA
+constexpr int kActBytes = 64 * 1024;             // staged core input per CTA
+#ifndef ST_GEMV_OCCUPANCY
+#define ST_GEMV_OCCUPANCY 1
+#endif
+#ifndef ST_GEMV_ILP
+#define ST_GEMV_ILP 2
+#endif
+constexpr int kCtasPerSm = ST_GEMV_OCCUPANCY;    // measured: a second resident CTA (the next launch) gains nothing
+constexpr int kTilesInFlight = ST_GEMV_ILP;      // independent tile decodes per warp
 
 struct GemvArgs {
     LinearCall call;
@@ -71,7 +79,7 @@ __host__ __device__ inline void contributors(long long units, int grid, long lon
 }  // namespace
 
 template <int K, int CB>
-__global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs args) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const GemvArgs args) {
     extern __shared__ __align__(128) unsigned char smem[];
     const LinearCall& c = args.call;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -101,7 +109,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs 
     __syncthreads();
 #ifdef ST_TIMELINE
     auto stamp = [&](int slot) {
-        if (args.timeline && (threadIdx.x == 0 || (slot == 6 && threadIdx.x == 32 * kConsumers))) {
+        if (args.timeline && ((threadIdx.x == 0 && slot != 1 && slot != 5) || (slot == 6 && threadIdx.x == 32 * kConsumers) ||
+                              ((slot == 1 || slot == 5) && threadIdx.x == 32 * (kConsumers + 1)))) {
             unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
             args.timeline[(size_t)blockIdx.x * 8 + slot] = t;
             if (slot == 3) args.timeline[(size_t)blockIdx.x * 8 + 7] = (unsigned long long)clock64();
@@ -151,6 +160,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs 
 
     if (warp == kConsumers + 1) {
         // ---- epilogue warp: turns dumped accumulators into partial planes or outputs ------
+        // Everything a flush needs that does not depend on the accumulators (contributor
+        // range, output scales, bias) is resolved BEFORE the wait for the dump, while the
+        // decode warps are still busy; after the dump the critical path is one plane write,
+        // one release/acquire atomic and, for the last arriver, one batch of plane loads.
         pdl_wait_prior_grid();  // y, scratch and counters may belong to the prior grid
         int done = 0, flush = 0;
         while (done < my_units) {
@@ -159,27 +172,36 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs 
             done += len;
             if (!((hb0 + len == hblocks) || (done == my_units))) continue;
             const int buf = flush & 1;
-            named_barrier(2 + buf, kDumpThreads);  // all decode warps have dumped into `buf`
-            const float* f0 = fold_base + buf * 2048;
             const long long blk_lo = (long long)nb * hblocks, blk_hi = blk_lo + hblocks;
             const bool whole = mine.begin <= blk_lo && mine.end >= blk_hi;
             int first = cta, last = cta;
+            if (!whole) contributors(units, grid, blk_lo, blk_hi, first, last);
+            float sv[4], bs[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int cidx = nb * 128 + lane + 32 * j;
+                sv[j] = half_bits_to_float(c.w.svh[cidx]);
+                bs[j] = c.w.bias ? c.w.bias[cidx] : 0.0f;
+            }
+            // the first contributor of a block begins at or before the block, every other inside it
+            float* plane = args.partials + ((size_t)cta * 2 + (cta == first ? 1 : 0)) * rows * 128;
+
+            named_barrier(2 + buf, kDumpThreads);  // all decode warps have dumped into `buf`
+            const float* f0 = fold_base + buf * 2048;
             bool finish = whole;
             if (!whole) {
-                contributors(units, grid, blk_lo, blk_hi, first, last);
-                float* plane = args.partials + ((size_t)cta * 2 + (mine.begin > blk_lo ? 0 : 1)) * rows * 128;
                 for (int e = lane; e < rows * 128; e += 32)  // k-groups in ascending order
                     plane[e] = __fadd_rn(f0[e], f0[1024 + e]);
-                __threadfence();
                 __syncwarp();
                 unsigned int seen = 0;
-                if (lane == 0) seen = atomicAdd(&args.counters[nb], 1u);
+                if (lane == 0)  // release: the plane is visible before the count; acquire: so are the others'
+                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;"
+                                 : "=r"(seen) : "l"(args.counters + nb) : "memory");
                 seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
+                __syncwarp();  // every lane's later plane loads are ordered after lane 0's acquire
+                stamp(1);
                 finish = (seen == (unsigned int)(last - first));
-                if (finish) {
-                    if (lane == 0) args.counters[nb] = 0;
-                    __threadfence();
-                }
+                if (finish && lane == 0) args.counters[nb] = 0;  // visible at grid end, before any later launch
             }
             if (finish) {
                 for (int r = 0; r < rows; ++r) {
@@ -189,19 +211,32 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs 
                         for (int j = 0; j < 4; ++j)
                             v[j] = __fadd_rn(0.f, __fadd_rn(f0[r * 128 + lane + 32 * j], f0[1024 + r * 128 + lane + 32 * j]));
                     } else {
-                        for (int p = first; p <= last; ++p) {  // ascending K order
-                            const int slot = cta_range(units, grid, p).begin > blk_lo ? 0 : 1;
-                            const float* plane = args.partials + ((size_t)p * 2 + slot) * rows * 128 + r * 128;
+                        for (int p0 = first; p0 <= last; p0 += 8) {  // ascending K order, eight planes in flight
+                            float t[8][4];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) v[j] = __fadd_rn(v[j], __ldcg(plane + lane + 32 * j));
+                            for (int q = 0; q < 8; ++q) {
+                                const int p = p0 + q;
+                                const float* src = args.partials + ((size_t)p * 2 + (p == first ? 1 : 0)) * rows * 128 + r * 128;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) t[q][j] = p <= last ? __ldcg(src + lane + 32 * j) : 0.0f;
+                            }
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                if (p0 + q <= last) {
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) v[j] = __fadd_rn(v[j], t[q][j]);
+                                }
                         }
                     }
                     hadamard128_warp(v, lane);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const int cidx = nb * 128 + lane + 32 * j;
-                        float* out = c.y + (long long)r * c.y_stride + cidx;
-                        *out = finish_output(v[j], c.w.svh[cidx], c.w.bias, cidx, c.alpha, c.beta, out);
+                        float* out = c.y + (long long)r * c.y_stride + nb * 128 + lane + 32 * j;
+                        float value = __fmul_rn(v[j], sv[j]);
+                        if (c.w.bias) value = __fadd_rn(value, bs[j]);
+                        value = __fmul_rn(value, c.alpha);
+                        if (c.beta != 0.0f) value = __fadd_rn(value, __fmul_rn(c.beta, *out));
+                        *out = value;
                     }
                 }
             }
@@ -225,6 +260,36 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs 
     __half* act_h = reinterpret_cast<__half*>(act);
     const int col = ctile * 16 + (lane >> 2), r0 = 2 * (lane & 3);
 
+    // One H128 block of one row through the input stages, written in B-fragment order:
+    // act[((slot*rows + r)*8 + kt)*4 + q] = {half2(k0,k0+1), half2(k0+8,k0+9)}, k0 = 2q
+    auto stage_block = [&](int r, int hb, int slot) {
+        const float* xr = c.x + (long long)r * c.x_stride + (size_t)hb * 128;
+        const uint16_t* su = c.w.suh + (size_t)hb * 128;
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = __half2float(scale_input(xr[lane + 32 * j], su[lane + 32 * j]));
+        hadamard128_warp(v, lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = lane + 32 * j, kt = e >> 4, kk = e & 15;
+            const int q = (kk & 7) >> 1, hi = kk >> 3, lo = kk & 1;
+            act_h[((((size_t)slot * rows + r) * 8 + kt) * 4 + q) * 4 + hi * 2 + lo] = __float2half_rn(v[j]);
+        }
+    };
+    // Resident mode: the whole core input fits the staging area, so every H128 block this
+    // CTA's range touches is staged exactly once, at its own slot, before the loop starts.
+    const bool resident = hblocks <= args.act_blocks;
+    if (resident) {
+        const int need = my_units < hblocks ? my_units : hblocks;
+        const int hb_first = (int)(mine.begin % hblocks);
+        for (int item = warp; item < rows * need; item += kConsumers) {
+            int hb = hb_first + item % need;
+            if (hb >= hblocks) hb -= hblocks;
+            stage_block(item / need, hb, hb);
+        }
+        named_barrier(1, kConsumers * 32);
+    }
+
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     bool ok = true;
     int done = 0, flush = 0;
@@ -232,25 +297,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs 
         int nb, hb0, len;
         segment(done, nb, hb0, len);
 
-        // input stages for H128 blocks [hb0, hb0+len), written in B-fragment order:
-        // act[((blk*rows + r)*8 + kt)*4 + q] = {half2(k0,k0+1), half2(k0+8,k0+9)}, k0 = 2q
-        named_barrier(1, kConsumers * 32);  // previous chunk's readers are done
-        for (int item = warp; item < rows * len; item += kConsumers) {
-            const int r = item / len, blk = item % len;
-            const float* xr = c.x + (long long)r * c.x_stride + (size_t)(hb0 + blk) * 128;
-            const uint16_t* su = c.w.suh + (size_t)(hb0 + blk) * 128;
-            float v[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = __half2float(scale_input(xr[lane + 32 * j], su[lane + 32 * j]));
-            hadamard128_warp(v, lane);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int e = lane + 32 * j, kt = e >> 4, kk = e & 15;
-                const int q = (kk & 7) >> 1, hi = kk >> 3, lo = kk & 1;
-                act_h[((((size_t)blk * rows + r) * 8 + kt) * 4 + q) * 4 + hi * 2 + lo] = __float2half_rn(v[j]);
-            }
+        // chunked mode: input stages for H128 blocks [hb0, hb0+len) into slots 0..len-1
+        if (!resident) {
+            named_barrier(1, kConsumers * 32);  // previous chunk's readers are done
+            for (int item = warp; item < rows * len; item += kConsumers) stage_block(item / len, hb0 + item % len, item % len);
+            named_barrier(1, kConsumers * 32);
         }
-        named_barrier(1, kConsumers * 32);
         if (done == 0) stamp(3);
 
         // this warp group takes the units of its parity (ring slots alternate with them)
@@ -260,15 +312,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs 
             if (!ok) break;
             const uint32_t* tiles =
                 reinterpret_cast<const uint32_t*>(ring + (size_t)st * kStage) + ctile * (8 * K);
-            const uint2* bsrc = act_lane + (size_t)b * rows * 32;
+            const uint2* bsrc = act_lane + (size_t)(resident ? hb0 + b : b) * rows * 32;
 #pragma unroll
-            for (int kt = 0; kt < 8; kt += 2) {  // two independent tiles in flight
-                uint32_t fa[4], fb[4];
-                decode_tile_frag<K, CB>(tiles + kt * 8 * (8 * K), geom, fa);
-                decode_tile_frag<K, CB>(tiles + (kt + 1) * 8 * (8 * K), geom, fb);
-                const uint2 ba = bsrc[kt * 4], bb = bsrc[(kt + 1) * 4];
-                mma_16816(acc[0], fa, ba.x, ba.y);
-                mma_16816(acc[1], fb, bb.x, bb.y);
+            for (int kt = 0; kt < 8; kt += kTilesInFlight) {  // independent tiles in flight
+                uint32_t f[kTilesInFlight][4];
+                uint2 bf[kTilesInFlight];
+#pragma unroll
+                for (int q = 0; q < kTilesInFlight; ++q) {
+                    decode_tile_frag<K, CB>(tiles + (kt + q) * 8 * (8 * K), geom, f[q]);
+                    bf[q] = bsrc[(kt + q) * 4];
+                }
+#pragma unroll
+                for (int q = 0; q < kTilesInFlight; ++q) mma_16816(acc[q & 1], f[q], bf[q].x, bf[q].y);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * st);
@@ -309,7 +364,10 @@ GemvPlan plan_gemv(const DeviceWeights& w, int rows, int sm_count) {
     const int per_cta = (int)((units + grid - 1) / grid);
     int act_blocks = kActBytes / (256 * rows);
     if (act_blocks > hblocks) act_blocks = hblocks;
-    int stages = (96 * 1024) / stage_bytes(w.bits);
+    const int ring_budget = 200 * 1024 - 16384 - 512 - act_blocks * 256 * rows;
+    int stages = ring_budget / stage_bytes(w.bits);
+    const int want = (128 * 1024) / stage_bytes(w.bits);  // enough bytes in flight per SM to cover HBM latency
+    if (stages > want) stages = want;
     if (stages > per_cta) stages = per_cta;
     if (stages > 28) stages = 28;
     if (stages < 1) stages = 1;

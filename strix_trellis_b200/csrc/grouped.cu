@@ -261,40 +261,77 @@ cudaError_t launch_swiglu(const float* gate, const float* up, float* hidden, int
     return cudaGetLastError();
 }
 
-// One thread per token: a row is valid when its ids are in range and distinct and its scores
-// are finite and non-negative (src/tp_moe_routes.hpp:46-61).  Slots of invalid rows run nothing.
-__global__ void moe_route_kernel(const unsigned int* __restrict__ ids, const float* __restrict__ scores,
-                                 int tokens, int top_k, const MoeBankEntry* __restrict__ bank, int bank_count,
-                                 GroupedProblem* gate_up, GroupedProblem* down, int* row_valid) {
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= tokens) return;
-    bool valid = true;
-    for (int s = 0; s < top_k && valid; ++s) {
-        const unsigned int id = ids[t * top_k + s];
-        const float sc = scores[t * top_k + s];
-        if (id >= (unsigned int)bank_count || !(sc >= 0.0f && sc <= 3.402823466e+38f)) valid = false;
-        for (int q = 0; q < s && valid; ++q)
-            if (ids[t * top_k + q] == id) valid = false;
-    }
-    row_valid[t] = valid ? 1 : 0;
-    for (int s = 0; s < top_k; ++s) {
-        const int p = t * top_k + s;
-        const unsigned int id = valid ? ids[p] : 0u;
-        gate_up[2 * p].rows = gate_up[2 * p + 1].rows = valid ? 1 : 0;
-        down[p].rows = (valid && scores[p] != 0.0f) ? 1 : 0;
-        if (valid) {
-            gate_up[2 * p].w = bank[id].gate;
-            gate_up[2 * p + 1].w = bank[id].up;
-            down[p].w = bank[id].down;
+// Device-side routing, one CTA.  A row is valid when its ids are in range and distinct and
+// its scores are finite and non-negative (src/tp_moe_routes.hpp:46-61); slots of invalid
+// rows run nothing.  Valid routes are grouped by expert into problems of up to eight rows,
+// so an expert's weights are streamed once per eight routed rows, not once per route.  A
+// row's result does not depend on which problem slot or row position carries it.
+// Zero-score routes are computed like any other; the combine skips them.
+__global__ void __launch_bounds__(1024) moe_route_kernel(const unsigned int* __restrict__ ids,
+                                                         const float* __restrict__ scores, int tokens, int top_k,
+                                                         const MoeBankEntry* __restrict__ bank, int bank_count,
+                                                         GroupedProblem* gate_up, GroupedProblem* down,
+                                                         int* row_valid) {
+    __shared__ int count[1024], first_problem[1024], cursor[1024], scan[1024];
+    const int tid = threadIdx.x, routes = tokens * top_k;
+    count[tid] = 0;
+    cursor[tid] = 0;
+    __syncthreads();
+    for (int t = tid; t < tokens; t += 1024) {
+        bool valid = true;
+        for (int s = 0; s < top_k && valid; ++s) {
+            const unsigned int id = ids[t * top_k + s];
+            const float sc = scores[t * top_k + s];
+            if (id >= (unsigned int)bank_count || !(sc >= 0.0f && sc <= 3.402823466e+38f)) valid = false;
+            for (int q = 0; q < s && valid; ++q)
+                if (ids[t * top_k + q] == id) valid = false;
         }
+        row_valid[t] = valid ? 1 : 0;
+        if (valid)
+            for (int s = 0; s < top_k; ++s) atomicAdd(&count[ids[t * top_k + s]], 1);
+    }
+    __syncthreads();
+    const int n = tid < bank_count ? count[tid] : 0;
+    const int problems = (n + kGroupRows - 1) / kGroupRows;
+    scan[tid] = problems;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {  // inclusive scan of problems per expert
+        const int add = tid >= off ? scan[tid - off] : 0;
+        __syncthreads();
+        scan[tid] += add;
+        __syncthreads();
+    }
+    const int begin = scan[tid] - problems, total = scan[1023];
+    first_problem[tid] = begin;
+    for (int k = 0; k < problems; ++k) {
+        const int q = begin + k;
+        const int rows = n - k * kGroupRows < kGroupRows ? n - k * kGroupRows : kGroupRows;
+        gate_up[2 * q].rows = gate_up[2 * q + 1].rows = down[q].rows = rows;
+        gate_up[2 * q].w = bank[tid].gate;
+        gate_up[2 * q + 1].w = bank[tid].up;
+        down[q].w = bank[tid].down;
+    }
+    for (int q = total + tid; q < routes; q += 1024)  // unused slots run nothing
+        gate_up[2 * q].rows = gate_up[2 * q + 1].rows = down[q].rows = 0;
+    __syncthreads();
+    for (int r = tid; r < routes; r += 1024) {
+        const int t = r / top_k;
+        if (!row_valid[t]) continue;
+        const int e = (int)ids[r];
+        const int pos = atomicAdd(&cursor[e], 1);
+        const int q = first_problem[e] + pos / kGroupRows, j = pos % kGroupRows;
+        gate_up[2 * q].x_row[j] = gate_up[2 * q + 1].x_row[j] = t;
+        gate_up[2 * q].y_row[j] = gate_up[2 * q + 1].y_row[j] = r;
+        down[q].x_row[j] = down[q].y_row[j] = r;
     }
 }
 
 cudaError_t launch_moe_route(const unsigned int* route_ids, const float* route_scores, int tokens, int top_k,
                              const MoeBankEntry* bank, int bank_count, GroupedProblem* gate_up, GroupedProblem* down,
                              int* row_valid, cudaStream_t stream) {
-    moe_route_kernel<<<(tokens + 63) / 64, 64, 0, stream>>>(route_ids, route_scores, tokens, top_k, bank, bank_count,
-                                                           gate_up, down, row_valid);
+    if (bank_count > 1024) return cudaErrorInvalidValue;
+    moe_route_kernel<<<1, 1024, 0, stream>>>(route_ids, route_scores, tokens, top_k, bank, bank_count, gate_up, down,
+                                             row_valid);
     return cudaGetLastError();
 }
 

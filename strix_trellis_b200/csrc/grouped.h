@@ -43,7 +43,8 @@ cudaError_t launch_swiglu(const float* gate, const float* up, float* hidden, int
                           long long out_stride, cudaStream_t stream);
 
 // Device-side routing for a persistent expert bank: validates each token's route row and
-// fills the per-route problem slots (one row each) from the bank table.
+// groups the valid routes by expert into problem slots of up to kGroupRows rows each
+// (slot tables hold tokens*top_k slots; unused ones get rows = 0).
 struct MoeBankEntry { DeviceWeights gate, up, down; };
 cudaError_t launch_moe_route(const unsigned int* route_ids, const float* route_scores, int tokens, int top_k,
                              const MoeBankEntry* bank, int bank_count, GroupedProblem* gate_up, GroupedProblem* down,

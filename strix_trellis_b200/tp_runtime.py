@@ -16,10 +16,16 @@ class RowParallelLinear:
     """Input (split-K) partition: rank r multiplies its slice of x by its K slice of the
     weights; all-reduce(sum) of the [rows, N] partial outputs."""
 
-    def __init__(self, ctx, tensor, rank, world, group=None, bias_rank=0):
+    def __init__(self, ctx, tensor, rank, world, group=None, bias_rank=0, full_inputs=None):
+        """`tensor` is the whole layer, or (with `full_inputs` = the layer's input size) this
+        rank's shard already cut, e.g. by a loader that reads only its own slice."""
         self.rank, self.world, self.group = rank, world, group
-        self.bounds = tp.h128_bounds(tensor.input_size, world)
-        self.weights = ctx.prepare(tp.rank_partition(tensor, "input", rank, world, bias_rank=bias_rank))
+        self.bounds = tp.h128_bounds(full_inputs or tensor.input_size, world)
+        shard = tensor if full_inputs else tp.rank_partition(tensor, "input", rank, world, bias_rank=bias_rank)
+        a0, a1 = self.bounds[rank]
+        if shard.input_size != a1 - a0:
+            raise ValueError("shard does not match this rank's input range")
+        self.weights = ctx.prepare(shard)
         self.plans = {}
 
     def local(self, x_full, y=None):
@@ -52,18 +58,39 @@ class ColumnParallelLinear:
     """Output partition (LM head): rank r owns an H128-aligned column range; all-gather of
     the logits (padded to the widest shard when the block count does not divide)."""
 
-    def __init__(self, ctx, tensor, rank, world, group=None):
+    def __init__(self, ctx, tensor, rank, world, group=None, full_outputs=None):
         self.rank, self.world, self.group = rank, world, group
-        self.bounds = tp.h128_bounds(tensor.output_size, world)
+        self.bounds = tp.h128_bounds(full_outputs or tensor.output_size, world)
         self.widths = [b - a for a, b in self.bounds]
-        self.weights = ctx.prepare(tp.rank_partition(tensor, "output", rank, world))
+        shard = tensor if full_outputs else tp.rank_partition(tensor, "output", rank, world)
+        if shard.output_size != self.widths[rank]:
+            raise ValueError("shard does not match this rank's output range")
+        self.weights = ctx.prepare(shard)
+        self.plans, self.outputs = {}, {}
 
     def local(self, x, y=None):
-        return self.weights.gemv(x, y)
+        """This rank's logits block; plans are frozen per (activation, output) buffer pair."""
+        if y is None:
+            y = self.outputs.get((x.shape[0], x.device))
+            if y is None:
+                y = self.outputs[(x.shape[0], x.device)] = torch.empty(
+                    (x.shape[0], self.weights.outputs), dtype=torch.float32, device=x.device)
+        key = (x.data_ptr(), tuple(x.shape), x.stride(0), y.data_ptr(), y.stride(0))
+        plan = self.plans.get(key)
+        if plan is None:
+            plan = self.plans[key] = DensePlan(self.weights, x, y)
+        plan.submit()
+        return y
 
     def forward(self, x):
         y = self.local(x)
         return y if self.world == 1 else tp.all_gather_columns(y, self.widths, self.group)
+
+    def close(self):
+        for plan in self.plans.values():
+            plan.close()
+        self.plans.clear()
+        self.weights.close()
 
 
 class ExpertParallelMoE:

@@ -68,7 +68,7 @@ def test_column_parallel_shards_concatenate_to_the_layer(ctx, world):
         shard = ColumnParallelLinear(ctx, as_tensor(layer), rank, world)
         pieces.append(host(shard.local(xd)))
         assert pieces[-1].shape[1] == shard.widths[rank]
-        shard.weights.close()
+        shard.close()
     got = np.concatenate(pieces, axis=1)
     gate(got, oracle_linear(layer, x), "column-parallel concat")
     full = ctx.prepare(layer)
