@@ -449,9 +449,13 @@ def run_gpu(args):
         avg_launch_us = ms_per_step * 1e3 / launches
         achieved = total_bytes / launches / avg_launch_us / 1e3  # GB/s per launch, one GPU
         traffic = None
-        tpath = ROOT / "profiles" / "gemv_k4_traffic.json"
+        # DRAM bytes per packed weight byte of this kernel, from the committed ncu summary of
+        # the 4096x14336 case; traffic grows in proportion to the packed bytes of a launch
+        tpath = ROOT / "profiles" / "gemv_fused_k4_r1_4096x14336.md"
         if tpath.exists():
-            traffic = json.loads(tpath.read_text()).get("dram_bytes_per_packed_byte")
+            for text in tpath.read_text().splitlines():
+                if text.strip().startswith("dram_bytes_per_packed_byte"):
+                    traffic = float(text.split("=")[1])
         base, _ = cpu_baseline() if world == 1 else (None, None)
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
