@@ -341,13 +341,26 @@ static bool tc_enabled() {
 GemmPlan plan_gemm_chunked(const DeviceWeights& w, int rows, int sm_count);
 cudaError_t launch_gemm_chunked(const LinearCall& call, int sm_count, void* workspace, cudaStream_t stream);
 
+// gemm_tc_pair.cu: two CTAs per 512 x 256 tile
+int gemm_pair_rows_padded(int rows);
+cudaError_t launch_gemm_pair(const LinearCall& call, const unsigned char* a_tiles, int sm_count, cudaStream_t stream);
+
+static bool pair_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("STRIX_B200_GEMM");
+        return e && e[0] == 'p';  // "pair" routes more than 256 rows to the two-CTA kernel; measured slower so far
+    }();
+    return on;
+}
+
 GemmPlan plan_gemm(const DeviceWeights& w, int rows, int sm_count) {
     if (!tc_enabled() || rows < 64) return plan_gemm_chunked(w, rows, sm_count);
     GemmPlan plan{};
-    const int m_pairs = (rows + kBM * kMT - 1) / (kBM * kMT);
-    plan.act_bytes = (size_t)m_pairs * kMT * kBM * w.inputs * 2;
+    const bool pair = rows > kBM * kMT && pair_enabled() && sm_count >= 2;
+    const int rows_padded = pair ? gemm_pair_rows_padded(rows) : (rows + kBM * kMT - 1) / (kBM * kMT) * (kBM * kMT);
+    plan.act_bytes = (size_t)rows_padded * w.inputs * 2;
     plan.workspace_bytes = align_up(plan.act_bytes);
-    plan.tile_m = kBM * kMT;
+    plan.tile_m = pair ? 2 * kBM * kMT : kBM * kMT;
     plan.tile_n = kBN;
     plan.sm_count = sm_count;
     plan.tensor_core = true;
@@ -385,8 +398,9 @@ static cudaError_t launch_tc_bits(const GemmArgs& a, int grid, cudaStream_t s) {
 cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* workspace, cudaStream_t stream) {
     if (!plan.tensor_core) return launch_gemm_chunked(call, plan.sm_count, workspace, stream);
     if (!workspace) return cudaErrorInvalidValue;
+    const bool pair = plan.tile_m == 2 * kBM * kMT;
     const int m_pairs = (call.rows + kBM * kMT - 1) / (kBM * kMT);
-    const int rows_padded = m_pairs * kBM * kMT;
+    const int rows_padded = pair ? gemm_pair_rows_padded(call.rows) : m_pairs * kBM * kMT;
     {
         const long long groups = (long long)rows_padded * (call.w.inputs / 128);
         const long long want = (groups + 7) / 8;
@@ -396,6 +410,7 @@ cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* work
         const cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
+    if (pair) return launch_gemm_pair(call, static_cast<const unsigned char*>(workspace), plan.sm_count, stream);
     GemmArgs args{};
     args.call = call;
     args.a_tiles = static_cast<const unsigned char*>(workspace);

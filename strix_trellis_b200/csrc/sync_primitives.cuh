@@ -48,6 +48,27 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
     if (status) atomicOr(status, fail_bit);
     return false;
 }
+// Cluster-scope variants for barriers that another CTA of the cluster arrives on.
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(2000u) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, unsigned int* status,
+                                                  unsigned int fail_bit) {
+    for (uint32_t i = 0; i < (1u << 17); ++i)
+        if (mbar_try_cluster(bar, parity)) return true;
+    if (status) atomicOr(status, fail_bit);
+    return false;
+}
+// Arrive on a barrier given by its shared::cluster address (see map_to_rank).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.  Source,
 // destination and size are multiples of 16 bytes.  No multicast.
 __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes,

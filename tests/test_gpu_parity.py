@@ -157,7 +157,7 @@ def test_gemm_small_rows(ctx, grid, rows):
         w.close()
 
 
-@pytest.mark.parametrize("rows", [64, 128, 200, 256, 300])
+@pytest.mark.parametrize("rows", [64, 128, 200, 256, 300, 513, 1030])
 def test_gemm_tensor_core_small_layers(ctx, grid, rows):
     """Rows >= 64 take the tcgen05 kernel: every rate and codebook, ragged row counts."""
     meta, outs = grid
