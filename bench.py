@@ -11,8 +11,8 @@ weights, ten times L2), so weights always come from HBM.  `value` is packed weig
 bytes per second (the reference's own definition, README.md:224-226) with inputs
 resident on the device and every call captured in one CUDA graph.  `e2e` is the same
 metric through the public C-ABI call (strix_linear_plan_submit) with HOST activations:
-every call's input is copied from pinned host memory and its output copied back
-inside the timed region.
+the step's activation rows are copied from pinned host memory before its calls and the
+output rows copied back to pinned host memory after them, inside the timed region.
 
 With N>1 (launched under torchrun) every rank runs the same workload on its own GPU
 (replicas: the plain GEMV has no cross-GPU exchange) and the value is the sum.
@@ -116,16 +116,19 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS to 1; the CPU arm uses every core this process may run on
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     per_step = []
     base = None
+    budget = max(2.0, 20.0 / max(args.steps + args.warmup, 1))
     for _ in range(args.warmup + args.steps):
-        base, _ = cpu_baseline(seconds_budget=max(2.0, 20.0 / max(args.steps + args.warmup, 1)))
+        base, _ = cpu_baseline(seconds_budget=budget)
         per_step.append(base["value"])
     vals = per_step[args.warmup:]
     value = float(np.mean(vals))
     base["value"] = value
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(budget * 1e3, 1), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 weights, f32 accumulate",
             "data": "synthetic", "config": {"workload": WORKLOAD, "host": "CPU contract, all host threads"},
             "cpu_baseline": base,
@@ -390,26 +393,53 @@ def run_gpu(args):
     ms_per_step = ms / args.steps
     value = world * total_bytes / (ms_per_step * 1e-3) / 1e9
 
-    # ---- end to end: host activations in, host outputs out, per call ---------------------
-    e2e_steps = max(1, min(args.steps, 3))
-    h2d = sum(len(g["plans"]) * g["hx"].numel() * 4 for g in groups)
-    d2h = sum(len(g["plans"]) * g["hy"].numel() * 4 for g in groups)
+    # ---- end to end: host activations in, host outputs out ---------------------------------
+    # The step's 96 activation rows sit in ONE pinned host buffer and its 96 output rows return
+    # to ONE pinned host buffer: [copy in, 96 x strix_linear_plan_submit, copy out] is the timed
+    # unit (captured once, replayed), every call reading its own slice and writing its own.
+    e2e_steps = max(1, min(args.steps, 10))
+    n_in = sum(len(g["weights"]) * g["layer"].inputs for g in groups) * ROWS
+    n_out = sum(len(g["weights"]) * g["layer"].outputs for g in groups) * ROWS
+    hx_all, hy_all = torch.empty(n_in).pin_memory(), torch.empty(n_out).pin_memory()
+    dx_all = torch.empty(n_in, dtype=torch.float32, device="cuda")
+    dy_all = torch.empty(n_out, dtype=torch.float32, device="cuda")
+    e2e_plans, oi, oo = [], 0, 0
     with torch.cuda.stream(stream):
-        def e2e_pass():
-            for g in groups:
-                for p in g["plans"]:
-                    g["x"].copy_(g["hx"], non_blocking=True)
-                    p.submit()
-                    g["hy"].copy_(g["y"], non_blocking=True)
-        e2e_pass()
+        for g in groups:
+            i_n, o_n = g["layer"].inputs * ROWS, g["layer"].outputs * ROWS
+            for w in g["weights"]:
+                hx_all[oi:oi + i_n] = g["hx"].reshape(-1)
+                e2e_plans.append(w.plan(dx_all[oi:oi + i_n].view(ROWS, -1), dy_all[oo:oo + o_n].view(ROWS, -1),
+                                        N.OP_GEMV, stream=stream))
+                oi, oo = oi + i_n, oo + o_n
+    h2d, d2h = n_in * 4, n_out * 4
+    e2e_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(e2e_graph, stream=stream):
+            dx_all.copy_(hx_all, non_blocking=True)
+            for p in e2e_plans:
+                p.submit()
+            hy_all.copy_(dy_all, non_blocking=True)
+        for _ in range(3):
+            e2e_graph.replay()
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(stream)
         for _ in range(e2e_steps):
-            e2e_pass()
+            e2e_graph.replay()
         b.record(stream)
         barrier()
         e2e_ms = a.elapsed_time(b) / e2e_steps
+    # the rows that came back are the rows the resident run produced (same weights, same input)
+    oo = 0
+    for g in groups:
+        o_n = g["layer"].outputs * ROWS
+        for _ in g["weights"]:
+            if not torch.equal(hy_all[oo:oo + o_n], g["y"].cpu().reshape(-1)):
+                raise SystemExit("end-to-end output row differs from the device-resident row")
+            oo += o_n
+    for p in e2e_plans:
+        p.close()
     e2e_t = torch.tensor([e2e_ms], device="cuda")
     if world > 1:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
