@@ -151,8 +151,8 @@ cudaError_t enqueue_linear(strix_context c, const st::LinearCall& call, void* wo
                            bool zero_counters, cudaStream_t stream) {
     if (call.rows <= 8) {
         const st::GemvPlan p = st::plan_gemv(call.w, call.rows, c->sm_count);
-        if (p.counter_bytes && zero_counters) {
-            const cudaError_t e = cudaMemsetAsync(workspace, 0, p.counter_bytes, stream);
+        if (zero_counters) {  // scratch of unknown content
+            const cudaError_t e = st::reset_gemv_scratch(workspace, p, stream);
             if (e != cudaSuccess) return e;
         }
         return st::launch_gemv(call, p, workspace, c->programmatic_launch, stream);

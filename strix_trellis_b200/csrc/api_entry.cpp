@@ -374,14 +374,12 @@ strix_status strix_linear_plan_create(strix_context c, const strix_matmul_desc* 
     strix_linear_plan_impl* p = new (std::nothrow) strix_linear_plan_impl{c, *d, make_call(c, *d, v), cs, v.rows};
     if (!p) return STRIX_ERROR_OUT_OF_MEMORY;
     if (v.rows && v.rows <= 8) {
-        // Arrival counters start at zero and every launch leaves them zero, so submit
-        // is a single kernel.  Zero them now and drain, so replays on any stream see zeros.
+        // The fold scratch starts empty and every launch leaves it empty, so submit is a
+        // single kernel.  Mark it now and drain, so replays on any stream find it empty.
         const st::GemvPlan gp = st::plan_gemv(p->call.w, v.rows, c->sm_count);
-        if (gp.counter_bytes) {
-            cudaError_t e = cudaMemsetAsync(d->workspace, 0, gp.counter_bytes, cs);
-            if (e == cudaSuccess) e = cudaStreamSynchronize(cs);
-            if (e != cudaSuccess) { delete p; return cuda_status(e); }
-        }
+        cudaError_t e = st::reset_gemv_scratch(d->workspace, gp, cs);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(cs);
+        if (e != cudaSuccess) { delete p; return cuda_status(e); }
     }
     ++d->weights->plan_refs;
     *out = p;

@@ -33,7 +33,7 @@ void release_plan(strix_tp_dense_plan_impl* p) {
 }
 
 // Scratch for one call.  Library-owned scratch hangs off the weights handle so that a
-// captured graph stays valid after the plan is gone; it is zeroed here once.
+// captured graph stays valid after the plan is gone; it is marked empty here once.
 strix_status provide_scratch(strix_context c, strix_weights w, int rows, void* caller, uint64_t caller_bytes,
                              uint64_t caller_offset, cudaStream_t cs, void*& out) {
     const st::GemvPlan gp = st::plan_gemv(w->device, rows, c->sm_count);
@@ -50,7 +50,7 @@ strix_status provide_scratch(strix_context c, strix_weights w, int rows, void* c
         if (e != cudaSuccess) { (void)cudaGetLastError(); return cuda_status(e); }
         try { w->plan_scratch.push_back(out); } catch (...) { (void)cudaFree(out); return STRIX_ERROR_OUT_OF_MEMORY; }
     }
-    e = cudaMemsetAsync(out, 0, gp.counter_bytes, cs);
+    e = st::reset_gemv_scratch(out, gp, cs);
     return cuda_status(e);
 }
 

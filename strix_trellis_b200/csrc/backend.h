@@ -71,6 +71,10 @@ struct GemvPlan {
 GemvPlan plan_gemv(const DeviceWeights& w, int rows, int sm_count);
 // `workspace` must be 256-byte aligned and hold counter_bytes + partial_bytes.  The
 // counters must be zero when the kernel starts; it leaves them zero.
+// Marks every partial-plane word of a GEMV scratch area "empty".  A completed launch leaves
+// the area empty again, so this is needed once per scratch area (plans) or before a launch
+// on scratch of unknown content (direct calls).
+cudaError_t reset_gemv_scratch(void* workspace, const GemvPlan& plan, cudaStream_t stream);
 cudaError_t launch_gemv(const LinearCall& call, const GemvPlan& plan, void* workspace,
                         bool programmatic_launch, cudaStream_t stream);
 

@@ -30,8 +30,8 @@ cudaError_t launch_gemm_chunked(const LinearCall& call, int sm_count, void* work
         part.x = call.x + (long long)begin * call.x_stride;
         part.y = call.y + (long long)begin * call.y_stride;
         const GemvPlan g = plan_gemv(call.w, part.rows, sm_count);
-        if (g.counter_bytes && !zeroed) {
-            const cudaError_t e = cudaMemsetAsync(workspace, 0, g.counter_bytes, stream);
+        if (!zeroed) {  // the first chunk is the largest: its scratch covers the others'
+            const cudaError_t e = reset_gemv_scratch(workspace, g, stream);
             if (e != cudaSuccess) return e;
             zeroed = true;
         }

@@ -15,11 +15,16 @@
 // activation rows are the B operand (n = row), so 1..8 rows cost the same tensor work.
 //
 // Fold: a column block that lies inside one CTA's range is finished by that CTA.  A
-// column block shared by several CTAs gets one partial plane per CTA in global scratch
-// and one arrival atomic per CTA; the last CTA to arrive folds the planes in ascending
-// K order from +0 (never in arrival order, never spinning -- the reference's scheme,
-// src/gemv_fused.hip:81-127) and applies the output stages.  All of that is done by a
-// separate epilogue warp: decode warps only drop their accumulators into a double-buffered
+// column block shared by several CTAs is finished by the CTA that holds its FIRST K range
+// -- the end of that CTA's own unit range, so it gets there when everybody else is done or
+// about to be.  The others publish one partial plane each in global scratch, word by word,
+// where a word is either the "empty" pattern (all ones, a NaN no sum produces) or a value:
+// no flag, no fence, no atomic.  The finishing CTA polls the words (bounded), adds the
+// planes in ascending K order from +0 with its own contribution first (never in arrival
+// order; the reference's order, src/gemv_fused.hip:81-127), marks them empty again and
+// applies the output stages.  Waits only point to higher CTA indices, all CTAs of the grid
+// are resident (grid <= SM count), and a wait that runs out reports kTimeoutFold.  All of that is done by
+// a separate epilogue warp: decode warps only drop their accumulators into a double-buffered
 // shared-memory area and move on, so no decode warp ever waits on global-memory latency.
 #include <cstdlib>
 
@@ -35,6 +40,7 @@ constexpr int kGroups = 2;                       // k-tile parities per column t
 constexpr int kConsumers = 8 * kGroups;          // decode warps
 constexpr int kThreads = (kConsumers + 2) * 32;  // + producer warp + epilogue warp
 constexpr int kDumpThreads = (kConsumers + 1) * 32;  // decode warps + epilogue warp
+constexpr uint32_t kEmptyWord = 0xFFFFFFFFu;      // a partial-plane word nobody has written yet
 constexpr int kActBytes = 64 * 1024;             // staged core input per CTA
 #ifndef ST_GEMV_OCCUPANCY
 #define ST_GEMV_OCCUPANCY 1
@@ -49,8 +55,7 @@ struct GemvArgs {
     LinearCall call;
     int stages;
     int act_blocks;            // H128 blocks of core input staged at a time
-    unsigned int* counters;    // [N/128], zero on entry, zero on exit
-    float* partials;           // [grid][2][rows][128]
+    float* partials;           // [grid][rows][128], every word empty on entry and on exit
 #ifdef ST_TIMELINE
     unsigned long long* timeline;
 #endif
@@ -164,7 +169,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
         // range, output scales, bias) is resolved BEFORE the wait for the dump, while the
         // decode warps are still busy; after the dump the critical path is one plane write,
         // one release/acquire atomic and, for the last arriver, one batch of plane loads.
-        pdl_wait_prior_grid();  // y, scratch and counters may belong to the prior grid
+        pdl_wait_prior_grid();  // y and scratch may belong to the prior grid
         int done = 0, flush = 0;
         while (done < my_units) {
             int nb, hb0, len;
@@ -183,51 +188,65 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
                 sv[j] = half_bits_to_float(c.w.svh[cidx]);
                 bs[j] = c.w.bias ? c.w.bias[cidx] : 0.0f;
             }
-            // the first contributor of a block begins at or before the block, every other inside it
-            float* plane = args.partials + ((size_t)cta * 2 + (cta == first ? 1 : 0)) * rows * 128;
+            // A CTA publishes at most one plane per launch: for the block its range begins inside.
+            uint32_t* plane = reinterpret_cast<uint32_t*>(args.partials) + (size_t)cta * rows * 128;
 
             named_barrier(2 + buf, kDumpThreads);  // all decode warps have dumped into `buf`
             const float* f0 = fold_base + buf * 2048;
-            bool finish = whole;
-            if (!whole) {
-                for (int e = lane; e < rows * 128; e += 32)  // k-groups in ascending order
-                    plane[e] = __fadd_rn(f0[e], f0[1024 + e]);
-                __syncwarp();
-                unsigned int seen = 0;
-                if (lane == 0)  // release: the plane is visible before the count; acquire: so are the others'
-                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;"
-                                 : "=r"(seen) : "l"(args.counters + nb) : "memory");
-                seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
-                __syncwarp();  // every lane's later plane loads are ordered after lane 0's acquire
+            if (!whole && cta != first) {
+                // contributor: publish the plane word by word (k-groups in ascending order); a
+                // real sum never has the empty pattern (an all-ones NaN), so no flag and no fence
+                for (int e = lane; e < rows * 128; e += 32)
+                    st_relaxed_gpu(plane + e, __float_as_uint(__fadd_rn(f0[e], f0[1024 + e])));
                 stamp(1);
-                finish = (seen == (unsigned int)(last - first));
-                if (finish && lane == 0) args.counters[nb] = 0;  // visible at grid end, before any later launch
-            }
-            if (finish) {
-                for (int r = 0; r < rows; ++r) {
-                    float v[4] = {0.f, 0.f, 0.f, 0.f};
-                    if (whole) {
+            } else {
+                // This CTA holds the FIRST K range of the block, which is the end of its own unit
+                // range: every other contributor finishes at about the same time or earlier.  It
+                // folds in ascending K order from +0: its own contribution (still in shared
+                // memory), then the others' planes.
+                bool folded = true;
+                for (int r = 0; r < rows && folded; ++r) {
+                    float v[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            v[j] = __fadd_rn(0.f, __fadd_rn(f0[r * 128 + lane + 32 * j], f0[1024 + r * 128 + lane + 32 * j]));
-                    } else {
-                        for (int p0 = first; p0 <= last; p0 += 8) {  // ascending K order, eight planes in flight
-                            float t[8][4];
+                    for (int j = 0; j < 4; ++j)
+                        v[j] = __fadd_rn(0.f, __fadd_rn(f0[r * 128 + lane + 32 * j], f0[1024 + r * 128 + lane + 32 * j]));
+                    for (int p0 = first + 1; p0 <= last && folded; p0 += 8) {  // eight planes in flight
+                        uint32_t t[8][4];
+                        bool have = false;
+                        for (uint32_t tries = 0; tries < (1u << 18) && !have; ++tries) {
+                            bool all = true;
 #pragma unroll
                             for (int q = 0; q < 8; ++q) {
                                 const int p = p0 + q;
-                                const float* src = args.partials + ((size_t)p * 2 + (p == first ? 1 : 0)) * rows * 128 + r * 128;
+                                const uint32_t* src =
+                                    reinterpret_cast<const uint32_t*>(args.partials) + (size_t)p * rows * 128 + r * 128;
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) t[q][j] = p <= last ? __ldcg(src + lane + 32 * j) : 0.0f;
-                            }
-#pragma unroll
-                            for (int q = 0; q < 8; ++q)
-                                if (p0 + q <= last) {
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) v[j] = __fadd_rn(v[j], t[q][j]);
+                                for (int j = 0; j < 4; ++j) {
+                                    t[q][j] = p <= last ? ld_relaxed_gpu(src + lane + 32 * j) : 0u;
+                                    all = all && t[q][j] != kEmptyWord;
                                 }
+                            }
+                            have = __all_sync(0xFFFFFFFFu, all);
+                        }
+                        if (!have) {  // bounded: report and leave this block unwritten
+                            if (lane == 0) atomicOr(c.status, kTimeoutFold);
+                            folded = false;
+                            break;
+                        }
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const int p = p0 + q;
+                            if (p <= last) {
+                                uint32_t* src = reinterpret_cast<uint32_t*>(args.partials) + (size_t)p * rows * 128 + r * 128;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    v[j] = __fadd_rn(v[j], __uint_as_float(t[q][j]));
+                                    st_relaxed_gpu(src + lane + 32 * j, kEmptyWord);  // empty again for the next launch
+                                }
+                            }
                         }
                     }
+                    if (!folded) break;
                     hadamard128_warp(v, lane);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -376,8 +395,8 @@ GemvPlan plan_gemv(const DeviceWeights& w, int rows, int sm_count) {
     plan.splits = (grid + nblocks - 1) / nblocks;  // typical K partitions of a column block
     plan.stages = stages;
     plan.smem_bytes = 16384 + 512 + (size_t)stages * stage_bytes(w.bits) + (size_t)act_blocks * 256 * rows;
-    plan.counter_bytes = align_up((size_t)nblocks * sizeof(unsigned int));
-    plan.partial_bytes = align_up((size_t)grid * 2 * rows * 128 * sizeof(float));
+    plan.counter_bytes = 0;  // the fold needs no counters
+    plan.partial_bytes = align_up((size_t)grid * rows * 128 * sizeof(float));
     return plan;
 }
 
@@ -418,6 +437,12 @@ static cudaError_t launch_bits(const GemvArgs& a, int g, size_t smem, bool pdl, 
     }
 }
 
+cudaError_t reset_gemv_scratch(void* workspace, const GemvPlan& plan, cudaStream_t stream) {
+    const size_t bytes = plan.counter_bytes + plan.partial_bytes;
+    if (!bytes) return cudaSuccess;
+    return cudaMemsetAsync(workspace, 0xFF, bytes, stream);
+}
+
 cudaError_t launch_gemv(const LinearCall& call, const GemvPlan& plan, void* workspace,
                         bool programmatic_launch, cudaStream_t stream) {
     if (call.rows < 1 || call.rows > 8 || !workspace) return cudaErrorInvalidValue;
@@ -425,7 +450,6 @@ cudaError_t launch_gemv(const LinearCall& call, const GemvPlan& plan, void* work
     args.call = call;
     args.stages = plan.stages;
     args.act_blocks = plan.act_blocks;
-    args.counters = static_cast<unsigned int*>(workspace);
     args.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + plan.counter_bytes);
 #ifdef ST_TIMELINE
     if (const char* t = getenv("STRIX_TL")) args.timeline = (unsigned long long*)strtoull(t, nullptr, 16);

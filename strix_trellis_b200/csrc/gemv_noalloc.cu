@@ -1,5 +1,5 @@
 // strix_b200_gemv_noalloc: the fused decode GEMV for callers that cannot supply or
-// obtain scratch memory.  The split-K scratch (arrival counters and partial planes)
+// obtain scratch memory.  The split-K scratch (partial planes)
 // lives in a fixed array inside the library image instead of a caller workspace.
 #include <mutex>
 
@@ -9,7 +9,7 @@ using namespace sapi;
 
 namespace {
 
-// Layout: [arrival counters: kMaxColumnBlocks x u32][partial planes: kMaxCtas x 2 x 8 rows
+// Layout: [reserved: kMaxColumnBlocks x u32][partial planes: kMaxCtas x 2 x 8 rows
 // x 128 floats].  Every GPU that loads the library carries this array until exit.
 constexpr size_t kMaxColumnBlocks = STRIX_B200_NOALLOC_MAX_OUTPUTS / 128;
 constexpr size_t kMaxCtas = 192;  // persistent CTAs (one per SM); B200 has 148
@@ -63,9 +63,9 @@ extern "C" strix_status strix_b200_gemv_noalloc(strix_context c, const strix_mat
     void* scratch = nullptr;
     cudaError_t e = scratch_address(c->device, &scratch);
     if (e != cudaSuccess) return cuda_status(e);
-    // The array keeps whatever the previous call left.  Counters must start at zero (a
-    // completed launch leaves them zero, an aborted one may not), planes are overwritten.
-    e = cudaMemsetAsync(scratch, 0, plan.counter_bytes, cs);
+    // The array keeps whatever the previous call left: a completed launch leaves every plane
+    // word empty, an aborted one may not, so the planes are marked empty before every call.
+    e = st::reset_gemv_scratch(scratch, plan, cs);
     if (e != cudaSuccess) return cuda_status(e);
     // launch_gemv places the planes right after plan.counter_bytes, inside the array
     return cuda_status(st::launch_gemv(make_call(c, *d, v), plan, scratch, c->programmatic_launch, cs));

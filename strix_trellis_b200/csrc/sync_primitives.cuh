@@ -11,6 +11,7 @@ enum : unsigned int {
     kTimeoutRingEmpty = 2u,   // producer waited for a stage that was never released
     kTimeoutDrain = 4u,       // copies still in flight at kernel exit
     kTimeoutTensorPipe = 8u,  // tcgen05 pipeline barrier
+    kTimeoutFold = 16u,       // split-K fold waited for a partial plane that never arrived
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -68,6 +69,16 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 // Arrive on a barrier given by its shared::cluster address (see map_to_rank).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Word-granular publication between CTAs of one grid: a 32-bit word is either the "empty"
+// pattern or a value, so neither a fence nor a flag is needed around it.
+__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_gpu(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.  Source,
 // destination and size are multiples of 16 bytes.  No multicast.
