@@ -105,6 +105,37 @@ def test_gemv_rank1_alpha_beta_and_poisoned_output(ctx, grid):
         w.close()
 
 
+def test_gemv_non_finite_inputs_fold_without_waiting(ctx):
+    """The split-K fold tells a published word from an unwritten one by its bit pattern (an
+    all-ones NaN).  NaN and infinite activations must come out as ordinary NaN/inf results:
+    no wait may run out (status word stays 0), other rows are unaffected, and the scratch is
+    left reusable (the same plan is submitted again with finite inputs)."""
+    layer = synthetic.make_layer(4096, 512, 4, seed=61, bias=True)  # 4 column blocks: every block is split
+    w = ctx.prepare(layer)
+    x = synthetic.make_activations(3, 4096, seed=62)
+    bad = x.copy()
+    bad[0, 5] = np.nan
+    bad[1, 700] = np.inf
+    bad[1, 701] = -np.inf
+    xd, y = dev(bad), torch.zeros((3, 512), device="cuda")
+    ws = torch.empty(max(w.workspace_bytes(xd, y), 256), dtype=torch.uint8, device="cuda")
+    plan = w.plan(xd, y, N.OP_GEMV, workspace=ws)
+    plan.submit()
+    torch.cuda.synchronize()
+    got = host(y)
+    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, 4, 2, x)
+    assert ctx.device_status() == 0
+    assert np.isnan(got[0]).all() and not np.isfinite(got[1]).any()
+    gate(got[2:], want[2:], "finite row beside non-finite rows")
+    xd.copy_(dev(x))
+    plan.submit()
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    gate(host(y), want, "same scratch after non-finite inputs")
+    plan.close()
+    w.close()
+
+
 def test_empty_call_validates_and_launches_nothing(ctx):
     layer = synthetic.make_layer(128, 128, 4, seed=5)
     w = ctx.prepare(layer)
