@@ -84,6 +84,7 @@ struct GemmPlan {
     size_t workspace_bytes;
     int tile_m, tile_n;
     int sm_count;
+    int k_splits;           // K partitions per output tile (> 1: raw partial accumulators in the workspace)
     bool tensor_core;       // tcgen05 prefill kernel selected (else 8-row GEMV chunks)
 };
 GemmPlan plan_gemm(const DeviceWeights& w, int rows, int sm_count);

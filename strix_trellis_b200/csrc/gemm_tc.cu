@@ -43,9 +43,8 @@ struct GemmArgs {
     const unsigned char* a_tiles;  // [M/128 padded][I/64][16 KB]
     int m_pairs;                   // ceil(rows / 256)
     int n_pairs;                   // ceil(column blocks / 2)
-#ifdef ST_DEBUG
-    int debug_mode;
-#endif
+    int k_splits;                  // K partitions per tile (1 = the epilogue finishes the outputs)
+    float* partials;               // [k_splits][rows padded to 256][N] raw accumulators when k_splits > 1
 };
 }  // namespace
 
@@ -87,8 +86,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
     const int kt64 = c.w.inputs / 64, ktiles16 = c.w.inputs / 16;
     const int nblocks = c.w.outputs / 128;
     // tiles ordered with the row pair fastest: CTAs that run together share a weight stripe
-    const int tiles = args.n_pairs * args.m_pairs;
+    // work item = (tile, K partition); partitions of a tile are neighbours in the order
+    const int splits = args.k_splits;
+    const int tiles = args.n_pairs * args.m_pairs * splits;
     const int my_tiles = tiles > (int)blockIdx.x ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    auto k_begin_of = [&](int t) { return kt64 * (t % splits) / splits; };
+    auto k_end_of = [&](int t) { return kt64 * (t % splits + 1) / splits; };
 
     unsigned char* ring = smem;
     float* staging = reinterpret_cast<float*>(ring + (size_t)kStagesTc * kStageBytesTc);
@@ -123,8 +126,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
             int it = 0;
             for (int lt = 0; lt < my_tiles && !s_abort; ++lt) {
                 const int t = (int)blockIdx.x + lt * (int)gridDim.x;
-                const int mp = t % args.m_pairs;
-                for (int ks = 0; ks < kt64; ++ks, ++it) {
+                const int mp = (t / splits) % args.m_pairs;
+                for (int ks = k_begin_of(t), ke = k_end_of(t); ks < ke; ++ks, ++it) {
                     const int st = it % kStagesTc;
                     if (it >= kStagesTc &&
                         !mbar_wait(empty + 8 * st, (uint32_t)((it / kStagesTc) - 1) & 1, c.status, kTimeoutTensorPipe)) {
@@ -155,7 +158,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                     break;
                 }
                 tc_fence_after_sync();
-                for (int ks = 0; ks < kt64 && !s_abort; ++ks, ++it) {
+                const int t = (int)blockIdx.x + lt * (int)gridDim.x;
+                const int kb = k_begin_of(t);
+                for (int ks = kb, ke = k_end_of(t); ks < ke && !s_abort; ++ks, ++it) {
                     const int st = it % kStagesTc;
                     const uint32_t par = (uint32_t)(it / kStagesTc) & 1;
                     if (!mbar_wait(full_a + 8 * st, par, c.status, kTimeoutTensorPipe) ||
@@ -171,7 +176,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                         const uint64_t adesc = umma_desc_k_major_sw128(base + mt * kTileBytes);
 #pragma unroll
                         for (int k4 = 0; k4 < kBK / 16; ++k4)  // +32 bytes per 16-element K step
-                            umma_f16(tmem_base + mt * kBN, adesc + 2 * k4, bdesc + 2 * k4, idesc, (ks | k4) != 0);
+                            umma_f16(tmem_base + mt * kBN, adesc + 2 * k4, bdesc + 2 * k4, idesc, ks != kb || k4 != 0);
                     }
                     umma_commit(empty + 8 * st);  // stage reusable once these MMAs have read it
                 }
@@ -184,7 +189,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
         float* stage = staging + (size_t)(warp - 2) * 16 * kStagingStride;
         for (int lt = 0; lt < my_tiles; ++lt) {
             const int t = (int)blockIdx.x + lt * (int)gridDim.x;
-            const int np = t / args.m_pairs, mp = t % args.m_pairs;
+            const int np = (t / splits) / args.m_pairs, mp = (t / splits) % args.m_pairs;
+            // K partitions leave raw accumulators; splitk_finish_kernel folds and finishes them
+            float* raw = splits > 1 ? args.partials + (size_t)(t % splits) * args.m_pairs * (kBM * kMT) * c.w.outputs
+                                    : nullptr;
             if (s_abort || !mbar_wait(tmem_full, (uint32_t)lt & 1, c.status, kTimeoutTensorPipe)) {
                 s_abort = 1;
                 break;
@@ -217,9 +225,16 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                         }
                         __syncwarp();
                         const int row_base = (mp * kMT + mt) * kBM + quarter * 32 + half * 16;
-#ifdef ST_DEBUG
-                        if (!(args.debug_mode & 2))
-#endif
+                        if (raw) {
+                            for (int r1 = 0; r1 < 16; ++r1) {
+                                const int row = row_base + r1;
+                                if (row < c.rows) {
+                                    float* out = raw + (size_t)row * c.w.outputs + nb * 128 + lane;
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) out[32 * j] = stage[r1 * kStagingStride + lane + 32 * j];
+                                }
+                            }
+                        } else
                         for (int r4 = 0; r4 < 16; r4 += 4) {  // four independent rows in flight
                             float v[4][4];
 #pragma unroll
@@ -261,16 +276,23 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
         const int n0 = d * 16 + (lane >> 2), kq = 2 * (lane & 3);
         const uint32_t o00 = sw128_offset(n0, kq), o01 = sw128_offset(n0, kq + 8);
         const uint32_t o10 = sw128_offset(n0 + 8, kq), o11 = sw128_offset(n0 + 8, kq + 8);
-        const int iters = my_tiles * kt64;
-        // (tile, K step) whose ring words are fetched next; advanced without divisions
+        int iters = 0;
+        for (int lt = 0; lt < my_tiles; ++lt) {
+            const int t = (int)blockIdx.x + lt * (int)gridDim.x;
+            iters += k_end_of(t) - k_begin_of(t);
+        }
+        // (work item, K step) whose ring words are fetched next
         int flt = 0, fks = 0, fetched = 0;
         const uint32_t* fcol = nullptr;
         bool fvalid = false;
+        int fke = 0;  // end of the K range of the work item being fetched
         auto fetch = [&](uint32_t (&w)[4][3]) {
-            if (fks == kt64) { fks = 0; ++flt; fcol = nullptr; }
+            if (fcol && fks == fke) { ++flt; fcol = nullptr; }
             if (!fcol) {
                 const int t = (int)blockIdx.x + flt * (int)gridDim.x;
-                const int nb = (t / args.m_pairs) * (kBN / 128) + cb;
+                fks = k_begin_of(t);
+                fke = k_end_of(t);
+                const int nb = ((t / splits) / args.m_pairs) * (kBN / 128) + cb;
                 fvalid = nb < nblocks;  // a padding stripe decodes nothing
                 fcol = c.w.packed + (((size_t)(fvalid ? nb : 0) * ktiles16) * 8 + ct) * (8 * K);
             }
@@ -293,9 +315,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                 break;
             }
             unsigned char* bt = ring + (size_t)st * kStageBytesTc + kMT * kTileBytes;
-#ifdef ST_DEBUG
-            if (!(args.debug_mode & 1))
-#endif
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {
                 uint32_t frag[4];
@@ -326,6 +345,33 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- launch 3 (only with K partitions): fold the raw partial accumulators in ascending K
+// order from +0 and apply the output stages; one warp per (row, 128-column block) ------------
+__global__ void splitk_finish_kernel(const float* __restrict__ partials, int splits, size_t plane, int rows,
+                                     int outputs, const uint16_t* __restrict__ svh, const float* __restrict__ bias,
+                                     float alpha, float beta, float* y, long long y_stride) {
+    const int lane = threadIdx.x & 31;
+    const int nblocks = outputs / 128;
+    const long long items = (long long)rows * nblocks;
+    for (long long g = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5); g < items;
+         g += (long long)gridDim.x * (blockDim.x >> 5)) {
+        const int row = (int)(g / nblocks), nb = (int)(g % nblocks);
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < splits; ++s) {
+            const float* src = partials + (size_t)s * plane + (size_t)row * outputs + nb * 128 + lane;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = __fadd_rn(v[j], src[32 * j]);
+        }
+        hadamard128_warp(v, lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int cidx = nb * 128 + lane + 32 * j;
+            float* out = y + (long long)row * y_stride + cidx;
+            *out = finish_output(v[j], svh[cidx], bias, cidx, alpha, beta, out);
+        }
     }
 }
 
@@ -361,6 +407,18 @@ GemmPlan plan_gemm(const DeviceWeights& w, int rows, int sm_count) {
     plan.act_bytes = (size_t)rows_padded * w.inputs * 2;
     plan.workspace_bytes = align_up(plan.act_bytes);
     plan.tile_m = pair ? 2 * kBM * kMT : kBM * kMT;
+    // One row tile leaves most SMs without a column tile: partition K so that every SM has work.
+    plan.k_splits = 1;
+    if (!pair && rows_padded == kBM * kMT) {
+        const int n_pairs = (w.outputs / 128 + kBN / 128 - 1) / (kBN / 128);
+        int splits = sm_count / n_pairs;
+        if (splits > 4) splits = 4;
+        while (splits > 1 && (w.inputs / kBK) / splits < 8) --splits;  // at least eight K steps per partition
+        if (splits > 1) {
+            plan.k_splits = splits;
+            plan.workspace_bytes += align_up((size_t)splits * rows_padded * w.outputs * sizeof(float));
+        }
+    }
     plan.tile_n = kBN;
     plan.sm_count = sm_count;
     plan.tensor_core = true;
@@ -416,18 +474,25 @@ cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* work
     args.a_tiles = static_cast<const unsigned char*>(workspace);
     args.m_pairs = m_pairs;
     args.n_pairs = (call.w.outputs / 128 + kBN / 128 - 1) / (kBN / 128);
-#ifdef ST_DEBUG
-    if (const char* e = getenv("STRIX_DBG")) args.debug_mode = atoi(e);
-#endif
-    const long long tiles = (long long)args.n_pairs * m_pairs;
+    args.k_splits = plan.k_splits;
+    args.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + align_up(plan.act_bytes));
+    const long long tiles = (long long)args.n_pairs * m_pairs * plan.k_splits;
     if (tiles > 0x3FFFFFFF) return cudaErrorInvalidValue;
     const int grid = (int)(tiles < plan.sm_count ? tiles : plan.sm_count);
+    cudaError_t e;
     switch (call.w.codebook) {
-    case CB_3INST: return launch_tc_bits<CB_3INST>(args, grid, stream);
-    case CB_MCG: return launch_tc_bits<CB_MCG>(args, grid, stream);
-    case CB_MUL1: return launch_tc_bits<CB_MUL1>(args, grid, stream);
+    case CB_3INST: e = launch_tc_bits<CB_3INST>(args, grid, stream); break;
+    case CB_MCG: e = launch_tc_bits<CB_MCG>(args, grid, stream); break;
+    case CB_MUL1: e = launch_tc_bits<CB_MUL1>(args, grid, stream); break;
     default: return cudaErrorInvalidValue;
     }
+    if (e != cudaSuccess || plan.k_splits == 1) return e;
+    const long long items = (long long)call.rows * (call.w.outputs / 128);
+    const long long want = (items + 7) / 8;
+    splitk_finish_kernel<<<(int)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(
+        args.partials, plan.k_splits, (size_t)rows_padded * call.w.outputs, call.rows, call.w.outputs, call.w.svh,
+        call.w.bias, call.alpha, call.beta, call.y, call.y_stride);
+    return cudaGetLastError();
 }
 
 }  // namespace st

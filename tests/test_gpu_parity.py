@@ -205,14 +205,21 @@ def test_gemm_tensor_core_small_layers(ctx, grid, rows):
         w.close()
 
 
+@pytest.mark.parametrize("rows", [100, 256, 512])
 @pytest.mark.parametrize("bits", [4, 5, 6])
-def test_gemm_tensor_core_prefill_shape(ctx, bits):
-    """4096 -> 1536 slice of the benchmark's fused-QKV-like layer, 512 token rows."""
-    layer = synthetic.make_layer(4096, 1536, bits, seed=90 + bits)
-    x = synthetic.make_activations(512, 4096, seed=91)
+def test_gemm_tensor_core_prefill_shape(ctx, bits, rows):
+    """4096 -> 1536 slice of the benchmark's fused-QKV-like layer.  Up to 256 rows there is one
+    row tile and K is partitioned over the idle SMs (raw partial accumulators, folded in
+    ascending K order by a finishing kernel); 512 rows take the unpartitioned route."""
+    layer = synthetic.make_layer(4096, 1536, bits, seed=90 + bits, bias=True)
+    x = synthetic.make_activations(rows, 4096, seed=91)
+    old = synthetic.rng_for(92).normal(0, 0.3, (rows, 1536)).astype(np.float32)
     w = ctx.prepare(layer)
-    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, None, bits, 2, x)
-    gate(host(w.gemm(dev(x))), want, f"prefill k{bits}")
+    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, bits, 2, x)
+    gate(host(w.gemm(dev(x))), want, f"prefill k{bits} rows {rows}")
+    y = dev(old.copy())
+    w.gemm(dev(x), y, alpha=0.5, beta=-1.0)
+    gate(host(y), ref.apply_alpha_beta(want, 0.5, -1.0, old), f"prefill k{bits} rows {rows} alpha/beta")
     w.close()
 
 
