@@ -4,7 +4,11 @@
 // own two activation tiles per K step and DECODES ONLY ITS OWN 128 COLUMNS of the weight
 // stage -- the MMA reads the other 128 from the partner's shared memory.  Against the
 // single-CTA kernel (gemm_tc.cu) every decoded weight now feeds twice as many rows, which
-// halves the decode work per flop, the limit of that kernel.
+// halves the decode work per flop, the limit of that kernel.  Measured at 8192 rows (K4,
+// 4096 -> 12288): 1230 us against 1070 us for the single-CTA kernel; with decode and epilogue
+// arithmetic both taken out the pair pipeline alone needs 840 us against 640 us, so the
+// stage hand-off between the two CTAs, not the decode, is what holds it back.  It is
+// therefore selected only on request (STRIX_B200_GEMM=pair).
 //
 // Per CTA: warp 0 activation producer (bulk copies), warp 1 MMA issuer (leader CTA) or relay
 // of "my activation stage landed" to the leader (partner CTA), warps 2-5 epilogue of the

@@ -50,18 +50,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
     return false;
 }
 // Cluster-scope variants for barriers that another CTA of the cluster arrives on.
+#ifndef ST_CLUSTER_WAIT_HINT
+#define ST_CLUSTER_WAIT_HINT 100
+#endif
+constexpr uint32_t kClusterWaitHintNs = ST_CLUSTER_WAIT_HINT;
 __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity), "r"(2000u) : "memory");
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(kClusterWaitHintNs) : "memory");
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, unsigned int* status,
                                                   unsigned int fail_bit) {
-    for (uint32_t i = 0; i < (1u << 17); ++i)
+    for (uint32_t i = 0; i < (1u << 21); ++i)  // short sleeps: about the same quarter second in total
         if (mbar_try_cluster(bar, parity)) return true;
     if (status) atomicOr(status, fail_bit);
     return false;
