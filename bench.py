@@ -255,6 +255,48 @@ def tp_case(torch, dist, ctx, stream, rank, world, rows_list=(1, 4, 8), reps=24)
     return out
 
 
+def ep_case(torch, dist, ctx, stream, rank, world, tokens_list=(1, 8, 64), experts=256, top_k=8, model=4096,
+            inter=2048, bits=2, reps=6):
+    """Benchmark configuration 5: 256 experts owned contiguously by the ranks, top-8 routing,
+    K2 gate/up/down; tokens live round-robin on the ranks; all-to-all dispatch of routed rows
+    to the owners, expert kernels, all-to-all back, combine at the home rank in slot order.
+    Microseconds per forward (device time between events on rank-local streams, max over
+    ranks; the dispatch exchanges its row counts through the host).  Routes rotate over four
+    seeded sets so that successive forwards touch different experts."""
+    from strix_trellis_b200 import synthetic
+    from strix_trellis_b200.tp_runtime import ExpertParallelMoE
+    proto = [synthetic.make_layer(model, inter, bits, seed=synthetic.BASE_SEED + 500, sigma=0.5),
+             synthetic.make_layer(model, inter, bits, seed=synthetic.BASE_SEED + 501, sigma=0.5),
+             synthetic.make_layer(inter, model, bits, seed=synthetic.BASE_SEED + 502, sigma=0.5)]
+    per = -(-experts // world)
+    mine = range(rank * per, min(experts, (rank + 1) * per))
+    bank = [tuple(ctx.prepare(l) for l in proto) for _ in mine]
+    out = {}
+    with torch.cuda.stream(stream):
+        for t in tokens_list:
+            sets = [synthetic.make_routes(t, experts, top_k, seed=synthetic.BASE_SEED + 520 + k) for k in range(4)]
+            x = synthetic.make_activations(t, model, seed=synthetic.BASE_SEED + 503)
+            home = [i for i in range(t) if i % world == rank]
+            xh = torch.from_numpy(x[home]).cuda() if home else torch.zeros((0, model), device="cuda")
+            ep = ExpertParallelMoE(ctx, bank, experts, rank, world, model, capacity=t * top_k)
+            turn = [0]
+
+            def forward():
+                turn[0] = (turn[0] + 1) % 4
+                ids, scores = sets[turn[0]]
+                return ep.forward(xh, ids[home].astype(np.int64).reshape(len(home), top_k), scores[home].reshape(len(home), top_k))
+            us = time_calls(torch, stream, forward, reps, warm=2)
+            tt = torch.tensor([us], device="cuda")
+            if world > 1:
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            out[f"T{t}"] = {"us": round(float(tt.item()), 1)}
+            ep.close()
+    for e in bank:
+        for w in e:
+            w.close()
+    return out
+
+
 def run_case(args):
     """A small fixed workload of one kernel, for profilers: a few launches, inputs larger
     than L2, a few hundred MB on the device."""
@@ -468,8 +510,10 @@ def run_gpu(args):
         if world > 1:
             dist.barrier()
         extra_tp = tp_case(torch, dist, ctx, stream, rank, world)
+        extra_ep = ep_case(torch, dist, ctx, stream, rank, world)
         if rank == 0:
             extra[f"tp_dense_K5_world{world}"] = extra_tp
+            extra[f"moe_256experts_top8_K2_world{world}"] = extra_ep
     status = ctx.device_status()
     if status:
         raise SystemExit(f"device status word {status:#x}: a bounded wait gave up; numbers invalid")
