@@ -50,9 +50,19 @@ strix_status strix_b200_core_exact(strix_context context, strix_weights weights,
 strix_status strix_b200_gemv_splits(strix_context context, strix_weights weights, uint32_t rows,
                                     uint32_t *out_splits);
 
+/* Work split of the fused GEMV for a layer of `inputs` x `outputs` on `grid` persistent CTAs
+ * (the kernel uses grid = min(SM count, units)): out[0], out[1] = the unit range CTA `cta`
+ * streams (a unit = one 128-column block x 128 inputs, column block major); out[2], out[3] =
+ * the first and last CTA that contribute to `column_block`.  A block with out[2] < out[3] is
+ * folded by CTA out[2], which waits for the partial planes of the CTAs above it.  Pure host
+ * arithmetic (no context, no device): lets the split and the direction of those waits be
+ * checked on a machine without a GPU.  No counterpart in the reference. */
+strix_status strix_b200_gemv_partition(uint64_t inputs, uint64_t outputs, uint32_t grid, uint32_t cta,
+                                       uint64_t column_block, uint64_t out[4]);
+
 /* Reads and clears the context's device status word.  Non-zero means that a bounded
  * wait inside a kernel gave up (bit 0 weight ring full-wait, bit 1 empty-wait, bit 2
- * drain at exit, bit 3 tensor pipeline); results of that launch are invalid.
+ * drain at exit, bit 3 tensor pipeline, bit 4 split-K fold); results of that launch are invalid.
  * Synchronises the device.  No counterpart in the reference (its kernels never wait). */
 strix_status strix_b200_device_status(strix_context context, uint32_t *out_bits);
 

@@ -1,5 +1,6 @@
 // Entry points declared in strix_trellis_b200.h: stage probes and runtime switches.
 #include "api_internal.h"
+#include "gemv_partition.h"
 
 using namespace sapi;
 
@@ -78,6 +79,29 @@ strix_status strix_b200_gemv_splits(strix_context c, strix_weights w, uint32_t r
     *out = 0;
     if (!c || !w || w->owner != c || rows < 1 || rows > 8) return STRIX_ERROR_INVALID_ARGUMENT;
     *out = (uint32_t)st::plan_gemv(w->device, (int)rows, c->sm_count).splits;
+    return STRIX_SUCCESS;
+}
+
+// Pure host arithmetic: no context, no device.
+strix_status strix_b200_gemv_partition(uint64_t inputs, uint64_t outputs, uint32_t grid, uint32_t cta,
+                                       uint64_t column_block, uint64_t out[4]) {
+    if (!out) return STRIX_ERROR_INVALID_ARGUMENT;
+    out[0] = out[1] = out[2] = out[3] = 0;
+    if (!inputs || !outputs || inputs % 128 || outputs % 128 || !grid || cta >= grid ||
+        inputs > (1ull << 31) || outputs > (1ull << 31))
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    const long long hblocks = (long long)(inputs / 128), nblocks = (long long)(outputs / 128);
+    if (column_block >= (uint64_t)nblocks || (uint64_t)grid > (uint64_t)(hblocks * nblocks))
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    const long long units = hblocks * nblocks;
+    const st::Range r = st::cta_range(units, (int)grid, (int)cta);
+    int first = 0, last = 0;
+    st::contributors(units, (int)grid, (long long)column_block * hblocks, (long long)(column_block + 1) * hblocks, first,
+                     last);
+    out[0] = (uint64_t)r.begin;
+    out[1] = (uint64_t)r.end;
+    out[2] = (uint64_t)first;
+    out[3] = (uint64_t)last;
     return STRIX_SUCCESS;
 }
 

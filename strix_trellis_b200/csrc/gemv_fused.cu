@@ -29,6 +29,7 @@
 #include <cstdlib>
 
 #include "backend.h"
+#include "gemv_partition.h"
 #include "hadamard.cuh"
 #include "sync_primitives.cuh"
 #include "trellis_decode.cuh"
@@ -63,24 +64,6 @@ struct GemvArgs {
 
 __host__ __device__ inline int stage_bytes(int bits) { return 2048 * bits; }
 
-struct Range { long long begin, end; };
-__host__ __device__ inline Range cta_range(long long units, int grid, int c) {
-    return Range{units * c / grid, units * (c + 1) / grid};
-}
-// CTAs whose ranges intersect the units [lo, hi) of one column block.
-__host__ __device__ inline void contributors(long long units, int grid, long long lo, long long hi,
-                                             int& first, int& last) {
-    int c = (int)(lo * grid / units);
-    if (c >= grid) c = grid - 1;
-    while (c > 0 && cta_range(units, grid, c).begin > lo) --c;
-    while (cta_range(units, grid, c).end <= lo) ++c;
-    first = c;
-    c = (int)((hi - 1) * grid / units);
-    if (c >= grid) c = grid - 1;
-    while (c + 1 < grid && cta_range(units, grid, c + 1).begin < hi) ++c;
-    while (cta_range(units, grid, c).begin >= hi) --c;
-    last = c;
-}
 }  // namespace
 
 template <int K, int CB>
