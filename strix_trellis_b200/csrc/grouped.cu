@@ -183,9 +183,17 @@ GroupedPlan plan_grouped(int inputs, int outputs, int max_bits, int problems, in
     GroupedPlan plan{};
     const int hblocks = inputs / 128, nblocks = outputs / 128;
     const int cap = 32;  // H128 blocks of K per CTA: 8 rows x 32 blocks x 256 B = 64 KB of core input
-    int splits = (hblocks + cap - 1) / cap;
-    // enough CTAs for two per SM across the whole group, but no more partitions than blocks
-    while ((long long)problems * nblocks * splits < 2LL * sm_count && splits * 2 <= hblocks && splits < 16) splits *= 2;
+    const int min_splits = (hblocks + cap - 1) / cap;
+    // Two CTAs fit an SM.  Among the K partition counts, take the one with the least
+    // (waves of CTAs) x (units per CTA + a fixed cost of about four units per CTA).
+    int splits = min_splits;
+    long long best = -1;
+    for (int s = min_splits; s <= hblocks && s <= 16; s *= 2) {
+        const long long ctas = (long long)problems * nblocks * s;
+        const long long waves = (ctas + 2LL * sm_count - 1) / (2LL * sm_count);
+        const long long cost = waves * ((hblocks + s - 1) / s + 4);
+        if (best < 0 || cost < best) { best = cost; splits = s; }
+    }
     const int per = (hblocks + splits - 1) / splits;
     int stages = (32 * 1024) / (2048 * max_bits);
     if (stages > per) stages = per;
