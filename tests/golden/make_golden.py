@@ -3,7 +3,7 @@
 Python package (python/strix_trellis in the reference tree).
 
 Run where the reference tree is mounted:
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <checkout of the reference project>
 
 Inputs are not stored: they are regenerated from seeds by
 strix_trellis_b200/synthetic.py, and their SHA-256 is recorded so drift is caught.
