@@ -160,6 +160,21 @@ def test_gemv_benchmark_shapes(ctx, bits, shape):
     w.close()
 
 
+@pytest.mark.parametrize("shape,rows", [((4096, 129280), 1), ((16384, 4096), 8)])
+def test_gemv_tensor_parallel_layer_shapes(ctx, shape, rows):
+    """The two dense layers of the tensor-parallel benchmark configuration, unsharded, K5:
+    the LM head (1010 column blocks, 218 units per CTA) and the 16384-input projection
+    (128 H128 blocks: at 8 rows the core input exceeds the staging area and is staged per
+    segment)."""
+    layer = synthetic.make_layer(shape[0], shape[1], 5, seed=300 + rows)
+    x = synthetic.make_activations(rows, shape[0], seed=301)
+    w = ctx.prepare(layer)
+    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, None, 5, 2, x)
+    gate(host(w.gemv(dev(x))), want, f"K5 {shape} rows {rows}")
+    assert ctx.device_status() == 0
+    w.close()
+
+
 def test_config1_against_reference_golden(ctx, golden_dir):
     meta = json.loads((golden_dir / "config1.json").read_text())
     gold = np.load(golden_dir / "config1.npz")
