@@ -117,15 +117,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
             const unsigned char* stream =
                 reinterpret_cast<const unsigned char*>(c.w.packed) + (size_t)mine.begin * kStage;
             int issued = 0;
+            int st = 0;             // ring slot of unit i and the parity of its previous use,
+            uint32_t prev_use = 1;  // stepped without divisions
             for (int i = 0; i < my_units; ++i) {
-                const int st = i % stages;
-                if (i >= stages &&
-                    !mbar_wait(empty0 + 8 * st, ((i / stages) - 1) & 1, c.status, kTimeoutRingEmpty))
-                    break;
+                if (i >= stages && !mbar_wait(empty0 + 8 * st, prev_use, c.status, kTimeoutRingEmpty)) break;
                 mbar_expect_tx(full0 + 8 * st, kStage);
                 bulk_load(smem_u32(ring + (size_t)st * kStage), stream + (size_t)i * kStage, kStage,
                           full0 + 8 * st);
                 issued = i + 1;
+                if (++st == stages) { st = 0; prev_use ^= 1; }
             }
             stamp(6);
             // Never leave the CTA with a copy still landing in its shared memory.
@@ -295,6 +295,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     bool ok = true;
     int done = 0, flush = 0;
+    int next = kgroup;  // the unit (relative to the range) this warp decodes next
+    int slot = kgroup % stages;
+    uint32_t use = (uint32_t)(kgroup / stages) & 1;
     while (done < my_units) {
         int nb, hb0, len;
         segment(done, nb, hb0, len);
@@ -308,10 +311,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
         if (done == 0) stamp(3);
 
         // this warp group takes the units of its parity (ring slots alternate with them)
-        for (int b = ((done & 1) == kgroup) ? 0 : 1; b < len && ok; b += 2) {
-            const int i = done + b, st = i % stages;
-            ok = mbar_wait(full0 + 8 * st, (i / stages) & 1, c.status, kTimeoutRingFull);
+        for (; next < done + len && ok; next += 2) {
+            const int b = next - done, st = slot;
+            ok = mbar_wait(full0 + 8 * st, use, c.status, kTimeoutRingFull);
             if (!ok) break;
+            slot += 2;  // ring slot and use parity of this warp's next unit, without divisions
+            while (slot >= stages) { slot -= stages; use ^= 1; }
             const uint32_t* tiles =
                 reinterpret_cast<const uint32_t*>(ring + (size_t)st * kStage) + ctile * (8 * K);
             const uint2* bsrc = act_lane + (size_t)(resident ? hb0 + b : b) * rows * 32;

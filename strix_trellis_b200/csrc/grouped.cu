@@ -34,9 +34,10 @@ __device__ __forceinline__ bool consume(const unsigned char* ring, int stage_str
                                         uint32_t empty0, const uint2* act_lane, int rows, int warp, int lane,
                                         unsigned int* status, float (&acc)[2][4]) {
     const LaneGeom<K> geom(lane);
-    for (int i = 0; i < nblk; ++i) {
-        const int st = i % stages;
-        if (!mbar_wait(full0 + 8 * st, (uint32_t)(i / stages) & 1, status, kTimeoutRingFull)) return false;
+    int st = 0;
+    uint32_t use = 0;  // ring slot and use parity of unit i, stepped without divisions
+    for (int i = 0; i < nblk; ++i, st = (st + 1 == stages ? 0 : st + 1), use ^= (st == 0)) {
+        if (!mbar_wait(full0 + 8 * st, use, status, kTimeoutRingFull)) return false;
         const uint32_t* tiles = reinterpret_cast<const uint32_t*>(ring + (size_t)st * stage_stride) + warp * (8 * K);
         const uint2* bsrc = act_lane + (size_t)i * rows * 32;
 #pragma unroll
