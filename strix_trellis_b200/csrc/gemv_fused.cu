@@ -251,6 +251,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     }
 
     // ---- decode warps -------------------------------------------------------------------
+    // Resident mode: the whole core input fits the staging area, so every H128 block this
+    // CTA's range touches is staged exactly once, at its own slot, before the loop starts.
+    // The input scales of a warp's first block are weights (immutable): they are fetched
+    // before the wait on the prior grid, so only the activation load follows it.
+    const bool resident = hblocks <= args.act_blocks;
+    const int need = my_units < hblocks ? my_units : hblocks;
+    const int hb_first = (int)(mine.begin % hblocks);
+    uint16_t su_first[4] = {0, 0, 0, 0};
+    if (resident && warp < rows * need) {
+        int hb = hb_first + warp % need;
+        if (hb >= hblocks) hb -= hblocks;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) su_first[j] = c.w.suh[(size_t)hb * 128 + lane + 32 * j];
+    }
     pdl_wait_prior_grid();  // x may belong to the prior grid
     stamp(2);
     const int ctile = warp & 7, kgroup = warp >> 3;
@@ -264,12 +278,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
 
     // One H128 block of one row through the input stages, written in B-fragment order:
     // act[((slot*rows + r)*8 + kt)*4 + q] = {half2(k0,k0+1), half2(k0+8,k0+9)}, k0 = 2q
-    auto stage_block = [&](int r, int hb, int slot) {
+    auto stage_block = [&](int r, int hb, int slot, bool have_scales) {
         const float* xr = c.x + (long long)r * c.x_stride + (size_t)hb * 128;
         const uint16_t* su = c.w.suh + (size_t)hb * 128;
         float v[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = __half2float(scale_input(xr[lane + 32 * j], su[lane + 32 * j]));
+        for (int j = 0; j < 4; ++j)
+            v[j] = __half2float(scale_input(xr[lane + 32 * j], have_scales ? su_first[j] : su[lane + 32 * j]));
         hadamard128_warp(v, lane);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -278,16 +293,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
             act_h[((((size_t)slot * rows + r) * 8 + kt) * 4 + q) * 4 + hi * 2 + lo] = __float2half_rn(v[j]);
         }
     };
-    // Resident mode: the whole core input fits the staging area, so every H128 block this
-    // CTA's range touches is staged exactly once, at its own slot, before the loop starts.
-    const bool resident = hblocks <= args.act_blocks;
     if (resident) {
-        const int need = my_units < hblocks ? my_units : hblocks;
-        const int hb_first = (int)(mine.begin % hblocks);
         for (int item = warp; item < rows * need; item += kConsumers) {
             int hb = hb_first + item % need;
             if (hb >= hblocks) hb -= hblocks;
-            stage_block(item / need, hb, hb);
+            stage_block(item / need, hb, hb, item == warp);
         }
         named_barrier(1, kConsumers * 32);
     }
@@ -305,7 +315,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
         // chunked mode: input stages for H128 blocks [hb0, hb0+len) into slots 0..len-1
         if (!resident) {
             named_barrier(1, kConsumers * 32);  // previous chunk's readers are done
-            for (int item = warp; item < rows * len; item += kConsumers) stage_block(item / len, hb0 + item % len, item % len);
+            for (int item = warp; item < rows * len; item += kConsumers) stage_block(item / len, hb0 + item % len, item % len, false);
             named_barrier(1, kConsumers * 32);
         }
         if (done == 0) stamp(3);
