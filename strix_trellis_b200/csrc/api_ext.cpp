@@ -94,10 +94,11 @@ strix_status strix_b200_gemv_partition(uint64_t inputs, uint64_t outputs, uint32
     if (column_block >= (uint64_t)nblocks || (uint64_t)grid > (uint64_t)(hblocks * nblocks))
         return STRIX_ERROR_INVALID_ARGUMENT;
     const long long units = hblocks * nblocks;
-    const st::Range r = st::cta_range(units, (int)grid, (int)cta);
+    if (units > 0x7FFFFFFF) return STRIX_ERROR_INVALID_ARGUMENT;
+    const st::Split split = st::make_split((int)units, (int)grid);
+    const st::Range r = st::cta_range(split, (int)cta);
     int first = 0, last = 0;
-    st::contributors(units, (int)grid, (long long)column_block * hblocks, (long long)(column_block + 1) * hblocks, first,
-                     last);
+    st::contributors(split, (int)(column_block * hblocks), (int)((column_block + 1) * hblocks), first, last);
     out[0] = (uint64_t)r.begin;
     out[1] = (uint64_t)r.end;
     out[2] = (uint64_t)first;

@@ -54,6 +54,7 @@ constexpr int kTilesInFlight = ST_GEMV_ILP;      // independent tile decodes per
 
 struct GemvArgs {
     LinearCall call;
+    Split split;               // unit range of every CTA (units / grid, units % grid)
     int stages;
     int act_blocks;            // H128 blocks of core input staged at a time
     float* partials;           // [grid][rows][128], every word empty on entry and on exit
@@ -73,10 +74,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rows = c.rows;
     const int hblocks = c.w.inputs / 128, nblocks = c.w.outputs / 128;
-    const long long units = (long long)hblocks * nblocks;
-    const int grid = (int)gridDim.x, cta = (int)blockIdx.x;
-    const Range mine = cta_range(units, grid, cta);
-    const int my_units = (int)(mine.end - mine.begin);
+    const int cta = (int)blockIdx.x;
+    const Range mine = cta_range(args.split, cta);
+    const int my_units = mine.end - mine.begin;
     const int stages = args.stages;
     constexpr int kStage = 2048 * K;
 
@@ -138,9 +138,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     // Segment walk shared by decode and epilogue warps: the CTA's unit range is cut at
     // column-block ends (where a contribution is flushed) and at the staging capacity.
     auto segment = [&](int done, int& nb, int& hb0, int& len) {
-        const long long u = mine.begin + done;
-        nb = (int)(u / hblocks);
-        hb0 = (int)(u % hblocks);
+        const int u = mine.begin + done;
+        nb = u / hblocks;
+        hb0 = u - nb * hblocks;
         len = my_units - done;
         if (len > hblocks - hb0) len = hblocks - hb0;
         if (len > args.act_blocks) len = args.act_blocks;
@@ -160,10 +160,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
             done += len;
             if (!((hb0 + len == hblocks) || (done == my_units))) continue;
             const int buf = flush & 1;
-            const long long blk_lo = (long long)nb * hblocks, blk_hi = blk_lo + hblocks;
+            const int blk_lo = nb * hblocks, blk_hi = blk_lo + hblocks;
             const bool whole = mine.begin <= blk_lo && mine.end >= blk_hi;
             int first = cta, last = cta;
-            if (!whole) contributors(units, grid, blk_lo, blk_hi, first, last);
+            if (!whole) contributors(args.split, blk_lo, blk_hi, first, last);
             float sv[4], bs[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     // before the wait on the prior grid, so only the activation load follows it.
     const bool resident = hblocks <= args.act_blocks;
     const int need = my_units < hblocks ? my_units : hblocks;
-    const int hb_first = (int)(mine.begin % hblocks);
+    const int hb_first = mine.begin % hblocks;
     uint16_t su_first[4] = {0, 0, 0, 0};
     if (resident && warp < rows * need) {
         int hb = hb_first + warp % need;
@@ -446,6 +446,9 @@ cudaError_t launch_gemv(const LinearCall& call, const GemvPlan& plan, void* work
     if (call.rows < 1 || call.rows > 8 || !workspace) return cudaErrorInvalidValue;
     GemvArgs args{};
     args.call = call;
+    const long long units = (long long)(call.w.inputs / 128) * (call.w.outputs / 128);
+    if (units > 0x7FFFFFFF || plan.grid < 1 || plan.grid > units) return cudaErrorInvalidValue;
+    args.split = make_split((int)units, plan.grid);
     args.stages = plan.stages;
     args.act_blocks = plan.act_blocks;
     args.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + plan.counter_bytes);
