@@ -87,11 +87,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     uint2* act = reinterpret_cast<uint2*>(ring + (size_t)stages * kStage);
 
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + stages);
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < stages; ++i) {
-            mbar_init(full0 + 8 * i, 1);
-            mbar_init(empty0 + 8 * i, 8);
-        }
+    if ((int)threadIdx.x < stages) {  // one thread per ring slot
+        mbar_init(full0 + 8 * threadIdx.x, 1);
+        mbar_init(empty0 + 8 * threadIdx.x, 8);
         mbar_fence_init();
     }
     __syncthreads();
