@@ -261,7 +261,7 @@ def ep_case(torch, dist, ctx, stream, rank, world, tokens_list=(1, 8, 64), exper
     K2 gate/up/down; tokens live round-robin on the ranks; all-to-all dispatch of routed rows
     to the owners, expert kernels, all-to-all back, combine at the home rank in slot order.
     Microseconds per forward (device time between events on rank-local streams, max over
-    ranks; the dispatch exchanges its row counts through the host).  Routes rotate over four
+    ranks; fixed-capacity exchange, no host synchronisation inside a forward).  Routes rotate over four
     seeded sets so that successive forwards touch different experts."""
     from strix_trellis_b200 import synthetic
     from strix_trellis_b200.tp_runtime import ExpertParallelMoE
@@ -278,13 +278,16 @@ def ep_case(torch, dist, ctx, stream, rank, world, tokens_list=(1, 8, 64), exper
             x = synthetic.make_activations(t, model, seed=synthetic.BASE_SEED + 503)
             home = [i for i in range(t) if i % world == rank]
             xh = torch.from_numpy(x[home]).cuda() if home else torch.zeros((0, model), device="cuda")
-            ep = ExpertParallelMoE(ctx, bank, experts, rank, world, model, capacity=t * top_k)
+            ep = ExpertParallelMoE(ctx, bank, experts, rank, world, model, max_tokens=-(-t // world), top_k=top_k)
+            on_device = [(torch.from_numpy(ids[home].astype(np.int64).reshape(len(home), top_k)).cuda(),
+                          torch.from_numpy(scores[home].reshape(len(home), top_k)).cuda()) for ids, scores in sets]
             turn = [0]
+
+            run = ep.capture(len(home)) if world == 1 else ep.forward  # one rank: the forward is one graph
 
             def forward():
                 turn[0] = (turn[0] + 1) % 4
-                ids, scores = sets[turn[0]]
-                return ep.forward(xh, ids[home].astype(np.int64).reshape(len(home), top_k), scores[home].reshape(len(home), top_k))
+                return run(xh, *on_device[turn[0]])
             us = time_calls(torch, stream, forward, reps, warm=2)
             tt = torch.tensor([us], device="cuda")
             if world > 1:

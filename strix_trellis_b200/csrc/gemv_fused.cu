@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     const LinearCall& c = args.call;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rows = c.rows;
-    const int hblocks = c.w.inputs / 128, nblocks = c.w.outputs / 128;
+    const int hblocks = c.w.inputs / 128;
     const int cta = (int)blockIdx.x;
     const Range mine = cta_range(args.split, cta);
     const int my_units = mine.end - mine.begin;

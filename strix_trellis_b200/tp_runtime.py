@@ -98,63 +98,93 @@ class ExpertParallelMoE:
     dispatch every (token, slot) row to the owner of its expert (all-to-all), run the
     owner's experts on the received rows (a device-routed plan with one route per row and
     score 1, so a row's output IS down_e(SwiGLU(...)) bit for bit), return the rows
-    (all-to-all) and combine at the token's home rank in ascending slot order from +0."""
+    (all-to-all) and combine at the token's home rank in ascending slot order from +0.
 
-    def __init__(self, ctx, local_experts, experts_total, rank, world, model, capacity, group=None):
+    The exchange uses a fixed capacity per rank pair (max_tokens * top_k rows, unused slots
+    carry an invalid expert id and run nothing), so a step needs no host synchronisation:
+    packing, the three collectives, the expert kernels and the combine are all enqueued."""
+
+    INVALID = 0x7FFFFFFF
+
+    def __init__(self, ctx, local_experts, experts_total, rank, world, model, max_tokens, top_k, group=None):
         self.ctx, self.rank, self.world, self.group = ctx, rank, world, group
         self.per_rank = -(-experts_total // world)
-        self.first = rank * self.per_rank
-        self.model, self.capacity = model, capacity
-        self.rows_in = torch.zeros((capacity, model), dtype=torch.float32, device="cuda")
-        self.rows_out = torch.zeros((capacity, model), dtype=torch.float32, device="cuda")
-        self.ids = torch.full((capacity,), 0x7FFFFFFF, dtype=torch.int32, device="cuda")  # invalid = idle slot
-        self.ones = torch.ones((capacity,), dtype=torch.float32, device="cuda")
-        self.plan = MoePlan(ctx, local_experts, self.rows_in, self.rows_out, self.ids, self.ones, device_routed=True)
+        self.model, self.top_k = model, top_k
+        self.cap = max_tokens * top_k  # rows one rank can send to (or receive from) one rank
+        rows = world * self.cap
+        f32 = dict(dtype=torch.float32, device="cuda")
+        self.send_x = torch.zeros((rows, model), **f32)
+        self.recv_x = self.send_x if world == 1 else torch.zeros((rows, model), **f32)
+        self.send_ids = torch.full((rows,), self.INVALID, dtype=torch.int32, device="cuda")
+        self.recv_ids = self.send_ids if world == 1 else torch.full((rows,), self.INVALID, dtype=torch.int32, device="cuda")
+        self.out_rows = torch.zeros((rows, model), **f32)
+        self.back = self.out_rows if world == 1 else torch.zeros((rows, model), **f32)
+        self.ones = torch.ones((rows,), **f32)
+        self.plan = MoePlan(ctx, local_experts, self.recv_x, self.out_rows, self.recv_ids, self.ones, device_routed=True)
+        self.graphs = []
 
     def forward(self, x, route_ids, route_scores, alpha=1.0):
-        """x [T_home, model] CUDA; route_ids/scores [T_home, top_k] host arrays (global ids)."""
+        """x [T, model] CUDA float32; route_ids [T, top_k] (global expert ids) and route_scores
+        [T, top_k] as CUDA tensors or host arrays; T <= max_tokens.  Returns y [T, model]."""
         import torch.distributed as dist
-        tokens, top_k = route_ids.shape
-        owner = route_ids // self.per_rank
-        order = np.argsort(owner.ravel(), kind="stable")          # routes grouped by owner rank
-        send_counts = np.bincount(owner.ravel(), minlength=self.world).astype(np.int64)
-        send_rows = x[torch.from_numpy((order // top_k).astype(np.int64)).cuda()]
-        send_ids = torch.from_numpy((route_ids.ravel()[order] % self.per_rank).astype(np.int32)).cuda()
+        ids = torch.as_tensor(np.asarray(route_ids) if not torch.is_tensor(route_ids) else route_ids).to("cuda").long()
+        scores = torch.as_tensor(np.asarray(route_scores, dtype=np.float32) if not torch.is_tensor(route_scores)
+                                 else route_scores).to("cuda", torch.float32)
+        tokens, top_k = ids.shape
+        if top_k != self.top_k or tokens * top_k > self.cap:
+            raise ValueError("routes exceed the capacity this layer was created for")
+        count = tokens * top_k
+        flat = ids.reshape(-1)
+        owner = flat // self.per_rank
+        order = torch.argsort(owner, stable=True)  # routes grouped by owner rank, slot order kept
+        sorted_owner = owner[order]
+        per_owner = torch.zeros(self.world, dtype=torch.long, device="cuda").scatter_add_(
+            0, owner, torch.ones_like(owner))
+        first = torch.cumsum(per_owner, 0) - per_owner
+        slot = sorted_owner * self.cap + (torch.arange(count, device="cuda") - first[sorted_owner])
+        self.send_ids.fill_(self.INVALID)
+        self.send_ids[slot] = (flat[order] % self.per_rank).int()
+        self.send_x[slot] = x[order // top_k]
         if self.world > 1:
-            counts_t = torch.from_numpy(send_counts).cuda()
-            recv_t = torch.empty_like(counts_t)
-            dist.all_to_all_single(recv_t, counts_t, group=self.group)
-            recv_counts = recv_t.cpu().numpy()
-        else:
-            recv_counts = send_counts
-        n_recv = int(recv_counts.sum())
-        if n_recv > self.capacity:
-            raise ValueError("more routed rows than the plan's capacity")
-        self.ids.fill_(0x7FFFFFFF)
-        if self.world > 1:
-            dist.all_to_all_single(self.rows_in[:n_recv], send_rows, recv_counts.tolist(), send_counts.tolist(),
-                                   group=self.group)
-            dist.all_to_all_single(self.ids[:n_recv], send_ids, recv_counts.tolist(), send_counts.tolist(),
-                                   group=self.group)
-        else:
-            self.rows_in[:n_recv] = send_rows
-            self.ids[:n_recv] = send_ids
+            dist.all_to_all_single(self.recv_x, self.send_x, group=self.group)
+            dist.all_to_all_single(self.recv_ids, self.send_ids, group=self.group)
         self.plan.submit()
-        back = torch.empty((order.size, self.model), dtype=torch.float32, device="cuda")
         if self.world > 1:
-            dist.all_to_all_single(back, self.rows_out[:n_recv], send_counts.tolist(), recv_counts.tolist(),
-                                   group=self.group)
-        else:
-            back.copy_(self.rows_out[:n_recv])
-        each = torch.empty((tokens * top_k, self.model), dtype=torch.float32, device="cuda")
-        each[torch.from_numpy(order.astype(np.int64)).cuda()] = back
+            dist.all_to_all_single(self.back, self.out_rows, group=self.group)
+        each = torch.empty((count, self.model), dtype=torch.float32, device="cuda")
+        each[order] = self.back[slot]
         each = each.view(tokens, top_k, self.model)
-        scores = torch.from_numpy(np.ascontiguousarray(route_scores, dtype=np.float32)).cuda()
         y = torch.zeros((tokens, self.model), dtype=torch.float32, device="cuda")
         for s in range(top_k):  # ascending slot order; mul and add round separately
             term = scores[:, s:s + 1] * each[:, s]
             y = torch.where(scores[:, s:s + 1] == 0, y, y + term)
         return y * alpha if alpha != 1.0 else y
 
+    def capture(self, tokens):
+        """Freezes forward() for `tokens` home tokens into a CUDA graph over static input
+        buffers (single-rank layers only: the collectives stay outside graphs).  Returns
+        run(x, ids, scores) -> y; y is a static buffer overwritten by the next run."""
+        if self.world != 1:
+            raise ValueError("capture is offered for single-rank layers")
+        x_in = torch.zeros((tokens, self.model), dtype=torch.float32, device="cuda")
+        ids_in = torch.zeros((tokens, self.top_k), dtype=torch.long, device="cuda")
+        sc_in = torch.zeros((tokens, self.top_k), dtype=torch.float32, device="cuda")
+        stream = torch.cuda.current_stream()
+        self.forward(x_in, ids_in, sc_in)  # warm-up outside the capture
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            y = self.forward(x_in, ids_in, sc_in)
+
+        def run(x, ids, scores):
+            x_in.copy_(x)
+            ids_in.copy_(ids)
+            sc_in.copy_(scores)
+            graph.replay()
+            return y
+        self.graphs.append(graph)
+        return run
+
     def close(self):
+        self.graphs.clear()
         self.plan.close()

@@ -85,7 +85,7 @@ def test_expert_parallel_single_rank_matches_the_block(ctx):
     ids, scores = synthetic.make_routes(tokens, n_exp, top_k, seed=9302)
     scores[2, 1] = 0.0
     want, _ = oracle_block(x, layers, ids, scores, 1.0, 0.0, np.zeros((tokens, model), np.float32))
-    ep = ExpertParallelMoE(ctx, ws, n_exp, 0, 1, model, capacity=tokens * top_k)
+    ep = ExpertParallelMoE(ctx, ws, n_exp, 0, 1, model, max_tokens=tokens, top_k=top_k)
     y = ep.forward(dev(x), ids.astype(np.int64), scores)
     torch.cuda.synchronize()
     gate(host(y), want, "expert-parallel (1 rank)", MOE_REL, MOE_NRMSE)
@@ -97,6 +97,15 @@ def test_expert_parallel_single_rank_matches_the_block(ctx):
     plan.submit()
     torch.cuda.synchronize()
     np.testing.assert_array_equal(host(y), host(y2))
+    # the same forward frozen into a graph, fed through its static buffers
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ep2 = ExpertParallelMoE(ctx, ws, n_exp, 0, 1, model, max_tokens=tokens, top_k=top_k)
+        run = ep2.capture(tokens)
+        y3 = run(dev(x), dev(ids.astype(np.int64)), dev(scores))
+        stream.synchronize()
+    np.testing.assert_array_equal(host(y3), host(y2))
+    ep2.close()
     plan.close()
     ep.close()
     for t in ws:
@@ -135,7 +144,7 @@ def _nccl_rank(rank, world, port, out):
     ids, scores = synthetic.make_routes(tokens, n_exp, top_k, seed=9302)
     scores[2, 1] = 0.0
     home = [t for t in range(tokens) if t % world == rank]  # tokens live round-robin on the ranks
-    ep = ExpertParallelMoE(ctx, ws, n_exp, rank, world, model, capacity=tokens * top_k)
+    ep = ExpertParallelMoE(ctx, ws, n_exp, rank, world, model, max_tokens=tokens, top_k=top_k)
     y_ep = ep.forward(torch.from_numpy(xm[home]).cuda(), ids[home].astype(np.int64), scores[home]).cpu().numpy()
     torch.cuda.synchronize()
     status = ctx.device_status()
