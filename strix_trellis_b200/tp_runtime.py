@@ -162,7 +162,8 @@ class ExpertParallelMoE:
 
     def capture(self, tokens):
         """Freezes forward() for `tokens` home tokens into a CUDA graph over static input
-        buffers (single-rank layers only: the collectives stay outside graphs).  Returns
+        buffers.  Single-rank layers only: with the collectives inside the capture a two-rank
+        run did not return, so multi-rank forwards stay eager.  Returns
         run(x, ids, scores) -> y; y is a static buffer overwritten by the next run."""
         if self.world != 1:
             raise ValueError("capture is offered for single-rank layers")
