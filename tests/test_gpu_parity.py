@@ -238,6 +238,35 @@ def test_gemm_tensor_core_prefill_shape(ctx, bits, rows):
     w.close()
 
 
+def test_gemm_full_prefill_size_sampled_rows_and_linearity(ctx):
+    """The benchmark's largest prefill case (8192 rows, 4096 -> 12288, K4) in one launch.  The
+    CPU contract is evaluated on a sample of rows spread over all row tiles (every 331st row and
+    the last one); the whole output is checked through properties that need no reference:
+    the fused GEMV of the same rows agrees within the gates, and alpha/beta act linearly."""
+    layer = synthetic.make_layer(4096, 12288, 4, seed=500, bias=True)
+    rows = 8192
+    x = synthetic.make_activations(rows, 4096, seed=501)
+    w = ctx.prepare(layer)
+    xd = dev(x)
+    y = w.gemm(xd)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    sample = sorted(set(list(range(0, rows, 331)) + [rows - 1]))
+    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, 4, 2, np.ascontiguousarray(x[sample]))
+    got = host(y[sample])
+    gate(got, want, "8192-row prefill, sampled rows")
+    # the GEMV route on eight of the sampled rows: another kernel, same contract
+    pick = sample[:8]
+    gate(host(w.gemv(dev(np.ascontiguousarray(x[pick])))), want[:8], "gemv on sampled rows")
+    # y2 = -0.5 * Linear(x) + 2 * y  ==  1.5 * y, elementwise within float32 rounding of the two products
+    y2 = y.clone()
+    w.gemm(xd, y2, alpha=-0.5, beta=2.0)
+    torch.cuda.synchronize()
+    expect = host(y) * np.float32(1.5)
+    np.testing.assert_allclose(host(y2), expect, rtol=2e-6, atol=1e-6 * float(np.abs(expect).max()))
+    w.close()
+
+
 def test_plan_submit_and_graph_replay(ctx):
     layer = synthetic.make_layer(4096, 1024, 5, seed=21, bias=True)
     w = ctx.prepare(layer)
