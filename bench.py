@@ -151,6 +151,37 @@ def time_calls(torch, stream, fn, reps, warm=3):
     return a.elapsed_time(b) * 1e3 / reps
 
 
+def gemv_sweep(torch, ctx, stream, shape=(4096, 14336), rates=(2, 3, 4, 5, 6), rows_list=(1, 8), copies=12):
+    """Rates and row counts of benchmark configuration 2 on its largest shape: microseconds per
+    launch and GB/s over packed bytes, `copies` device copies launched in turn as one graph
+    (12 x 14.7 MB at K2 is already larger than L2)."""
+    from strix_trellis_b200 import native as N, synthetic
+    out = {}
+    for bits in rates:
+        layer = synthetic.make_layer(shape[0], shape[1], bits, seed=synthetic.BASE_SEED + 800 + bits)
+        ws = [ctx.prepare(layer) for _ in range(copies)]
+        for rows in rows_list:
+            x = torch.from_numpy(synthetic.make_activations(rows, shape[0], seed=synthetic.BASE_SEED + 801)).cuda()
+            y = torch.empty((rows, shape[1]), dtype=torch.float32, device="cuda")
+            with torch.cuda.stream(stream):
+                plans = [w.plan(x, y, N.OP_GEMV, stream=stream) for w in ws]
+                for p in plans:
+                    p.submit()
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for p in plans:
+                        p.submit()
+            us = time_calls(torch, stream, graph.replay, 5) / copies
+            out[f"K{bits}_R{rows}"] = {"us": round(us, 2), "GBps": round(layer.packed_bytes / us / 1e3, 1)}
+            del graph
+            for p in plans:
+                p.close()
+        for w in ws:
+            w.close()
+    return out
+
+
 def gemm_case(torch, ctx, stream, rows_list, bits=4, inputs=4096, outputs=12288, reps=None):
     """Prefill GEMM of benchmark configuration 3 (4096 -> 12288): microseconds and TFLOP/s."""
     from strix_trellis_b200 import native as N, synthetic
@@ -510,6 +541,7 @@ def run_gpu(args):
             gemm = gemm_case(torch, ctx, stream, [128, 512, 2048, 8192])
             for v in gemm.values():
                 v["frac_of_measured_dense_peak"] = round(v["TFLOPs"] / gemm_peak, 3)
+            extra["gemv_4096x14336_rates_rows"] = gemv_sweep(torch, ctx, stream)
             extra["prefill_gemm_K4_4096x12288"] = gemm
             extra["moe_bank32_top8_K2_one_rank"] = moe_case(torch, ctx, stream, [1, 8, 64])
         if world > 1:

@@ -27,6 +27,7 @@
 // a separate epilogue warp: decode warps only drop their accumulators into a double-buffered
 // shared-memory area and move on, so no decode warp ever waits on global-memory latency.
 #include <cstdlib>
+#include <type_traits>
 
 #include "backend.h"
 #include "gemv_partition.h"
@@ -67,7 +68,10 @@ __host__ __device__ inline int stage_bytes(int bits) { return 2048 * bits; }
 
 }  // namespace
 
-template <int K, int CB>
+// MULTI selects the code for more than one activation row (several staging items per warp in
+// flight, fold sums in shared memory); the one-row instantiation carries none of it, which
+// keeps the latency-critical head and tail of the decode case as short as they can be.
+template <int K, int CB, bool MULTI>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const GemvArgs args) {
     extern __shared__ __align__(128) unsigned char smem[];
     const LinearCall& c = args.call;
@@ -184,50 +188,104 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
                 // This CTA holds the FIRST K range of the block, which is the end of its own unit
                 // range: every other contributor finishes at about the same time or earlier.  It
                 // folds in ascending K order from +0: its own contribution (still in shared
-                // memory), then the others' planes.
+                // memory), then the others' planes.  The sums are kept in shared memory (each lane
+                // only ever touches its own words) and the (row, plane) pairs are polled eight at a
+                // time, plane index fastest, so several rows share one round trip to L2.
+                float* accum = fold_base + buf * 2048;
+                const int planes = last - first, items = rows * planes;
                 bool folded = true;
-                for (int r = 0; r < rows && folded; ++r) {
+                if (!MULTI) {
+                    // one row: the sums stay in registers (the shortest tail for the decode case)
                     float v[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        v[j] = __fadd_rn(0.f, __fadd_rn(f0[r * 128 + lane + 32 * j], f0[1024 + r * 128 + lane + 32 * j]));
-                    for (int p0 = first + 1; p0 <= last && folded; p0 += 8) {  // eight planes in flight
+                        v[j] = __fadd_rn(0.f, __fadd_rn(f0[lane + 32 * j], f0[1024 + lane + 32 * j]));
+                    for (int p0 = first + 1; p0 <= last && folded; p0 += 8) {
                         uint32_t t[8][4];
                         bool have = false;
                         for (uint32_t tries = 0; tries < (1u << 18) && !have; ++tries) {
                             bool all = true;
 #pragma unroll
                             for (int q = 0; q < 8; ++q) {
-                                const int p = p0 + q;
                                 const uint32_t* src =
-                                    reinterpret_cast<const uint32_t*>(args.partials) + (size_t)p * rows * 128 + r * 128;
+                                    reinterpret_cast<const uint32_t*>(args.partials) + (size_t)(p0 + q) * 128 + lane;
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
-                                    t[q][j] = p <= last ? ld_relaxed_gpu(src + lane + 32 * j) : 0u;
+                                    t[q][j] = p0 + q <= last ? ld_relaxed_gpu(src + 32 * j) : 0u;
                                     all = all && t[q][j] != kEmptyWord;
                                 }
                             }
                             have = __all_sync(0xFFFFFFFFu, all);
                         }
-                        if (!have) {  // bounded: report and leave this block unwritten
+                        if (!have) {
                             if (lane == 0) atomicOr(c.status, kTimeoutFold);
                             folded = false;
                             break;
                         }
 #pragma unroll
                         for (int q = 0; q < 8; ++q) {
-                            const int p = p0 + q;
-                            if (p <= last) {
-                                uint32_t* src = reinterpret_cast<uint32_t*>(args.partials) + (size_t)p * rows * 128 + r * 128;
+                            if (p0 + q <= last) {
+                                uint32_t* src = reinterpret_cast<uint32_t*>(args.partials) + (size_t)(p0 + q) * 128 + lane;
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
                                     v[j] = __fadd_rn(v[j], __uint_as_float(t[q][j]));
-                                    st_relaxed_gpu(src + lane + 32 * j, kEmptyWord);  // empty again for the next launch
+                                    st_relaxed_gpu(src + 32 * j, kEmptyWord);
                                 }
                             }
                         }
                     }
-                    if (!folded) break;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) accum[lane + 32 * j] = v[j];
+                } else {
+                for (int e = lane; e < rows * 128; e += 32)
+                    accum[e] = __fadd_rn(0.f, __fadd_rn(accum[e], accum[1024 + e]));
+                int next_row = 0, next_plane = 0;  // the pair after the ones batched so far (no divisions)
+                for (int i0 = 0; i0 < items && folded; i0 += 8) {
+                    uint32_t* src[8];
+                    int row_of[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        row_of[q] = next_row;
+                        src[q] = reinterpret_cast<uint32_t*>(args.partials) +
+                                 ((size_t)(first + 1 + next_plane) * rows + next_row) * 128 + lane;
+                        if (i0 + q + 1 < items && ++next_plane == planes) { next_plane = 0; ++next_row; }
+                    }
+                    uint32_t t[8][4];
+                    bool have = false;
+                    for (uint32_t tries = 0; tries < (1u << 18) && !have; ++tries) {
+                        bool all = true;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                t[q][j] = i0 + q < items ? ld_relaxed_gpu(src[q] + 32 * j) : 0u;
+                                all = all && t[q][j] != kEmptyWord;
+                            }
+                        }
+                        have = __all_sync(0xFFFFFFFFu, all);
+                    }
+                    if (!have) {  // bounded: report and leave this block unwritten
+                        if (lane == 0) atomicOr(c.status, kTimeoutFold);
+                        folded = false;
+                        break;
+                    }
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        if (i0 + q < items) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                float* a = accum + row_of[q] * 128 + lane + 32 * j;
+                                *a = __fadd_rn(*a, __uint_as_float(t[q][j]));
+                                st_relaxed_gpu(src[q] + 32 * j, kEmptyWord);  // empty again for the next launch
+                            }
+                        }
+                    }
+                }
+                }
+                for (int r = 0; r < rows && folded; ++r) {
+                    float v[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[j] = accum[r * 128 + lane + 32 * j];
                     hadamard128_warp(v, lane);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -274,29 +332,57 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     __half* act_h = reinterpret_cast<__half*>(act);
     const int col = ctile * 16 + (lane >> 2), r0 = 2 * (lane & 3);
 
-    // One H128 block of one row through the input stages, written in B-fragment order:
-    // act[((slot*rows + r)*8 + kt)*4 + q] = {half2(k0,k0+1), half2(k0+8,k0+9)}, k0 = 2q
-    auto stage_block = [&](int r, int hb, int slot, bool have_scales) {
-        const float* xr = c.x + (long long)r * c.x_stride + (size_t)hb * 128;
-        const uint16_t* su = c.w.suh + (size_t)hb * 128;
-        float v[4];
+    // (row, H128 block) items through the input stages, written in B-fragment order:
+    // act[((slot*rows + r)*8 + kt)*4 + q] = {half2(k0,k0+1), half2(k0+8,k0+9)}, k0 = 2q.
+    // A warp keeps four items in flight so that their global loads overlap (eight rows of a
+    // 4096-input layer are 256 items, sixteen per warp).  where(item, r, hb, slot) names an item.
+    auto stage_items = [&](int n, bool first_scales_ready, auto&& where, auto width) {
+        constexpr int kInFlight = decltype(width)::value;
+        for (int base = warp; base < n; base += kInFlight * kConsumers) {
+            float xv[kInFlight][4];
+            uint16_t sc[kInFlight][4];
+            int rr[kInFlight], ss[kInFlight];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            v[j] = __half2float(scale_input(xr[lane + 32 * j], have_scales ? su_first[j] : su[lane + 32 * j]));
-        hadamard128_warp(v, lane);
+            for (int u = 0; u < kInFlight; ++u) {
+                const int item = base + u * kConsumers;
+                if (item < n) {
+                    int hb;
+                    where(item, rr[u], hb, ss[u]);
+                    const float* xr = c.x + (long long)rr[u] * c.x_stride + (size_t)hb * 128;
+                    const uint16_t* su = c.w.suh + (size_t)hb * 128;
+                    const bool ready = first_scales_ready && item == warp;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int e = lane + 32 * j, kt = e >> 4, kk = e & 15;
-            const int q = (kk & 7) >> 1, hi = kk >> 3, lo = kk & 1;
-            act_h[((((size_t)slot * rows + r) * 8 + kt) * 4 + q) * 4 + hi * 2 + lo] = __float2half_rn(v[j]);
+                    for (int j = 0; j < 4; ++j) {
+                        xv[u][j] = xr[lane + 32 * j];
+                        sc[u][j] = ready ? su_first[j] : su[lane + 32 * j];
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                if (base + u * kConsumers < n) {
+                    float v[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[j] = __half2float(scale_input(xv[u][j], sc[u][j]));
+                    hadamard128_warp(v, lane);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int e = lane + 32 * j, kt = e >> 4, kk = e & 15;
+                        const int q = (kk & 7) >> 1, hi = kk >> 3, lo = kk & 1;
+                        act_h[((((size_t)ss[u] * rows + rr[u]) * 8 + kt) * 4 + q) * 4 + hi * 2 + lo] = __float2half_rn(v[j]);
+                    }
+                }
+            }
         }
     };
     if (resident) {
-        for (int item = warp; item < rows * need; item += kConsumers) {
-            int hb = hb_first + item % need;
+        auto where = [&](int item, int& r, int& hb, int& slot) {
+            r = item / need;
+            hb = hb_first + item % need;
             if (hb >= hblocks) hb -= hblocks;
-            stage_block(item / need, hb, hb, item == warp);
-        }
+            slot = hb;
+        };
+        stage_items(rows * need, true, where, std::integral_constant<int, MULTI ? 4 : 1>{});
         named_barrier(1, kConsumers * 32);
     }
 
@@ -313,7 +399,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
         // chunked mode: input stages for H128 blocks [hb0, hb0+len) into slots 0..len-1
         if (!resident) {
             named_barrier(1, kConsumers * 32);  // previous chunk's readers are done
-            for (int item = warp; item < rows * len; item += kConsumers) stage_block(item / len, hb0 + item % len, item % len, false);
+            stage_items(rows * len, false, [&](int item, int& r, int& hb, int& slot) {
+                r = item / len;
+                slot = item % len;
+                hb = hb0 + slot;
+            }, std::integral_constant<int, MULTI ? 4 : 1>{});
             named_barrier(1, kConsumers * 32);
         }
         if (done == 0) stamp(3);
@@ -396,11 +486,11 @@ GemvPlan plan_gemv(const DeviceWeights& w, int rows, int sm_count) {
     return plan;
 }
 
-template <int K, int CB>
-static cudaError_t launch_one(const GemvArgs& args, int grid, size_t smem, bool pdl, cudaStream_t stream) {
+template <int K, int CB, bool MULTI>
+static cudaError_t launch_rows(const GemvArgs& args, int grid, size_t smem, bool pdl, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(gemv_fused_kernel<K, CB>,
+        const cudaError_t e = cudaFuncSetAttribute(gemv_fused_kernel<K, CB, MULTI>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
         if (e != cudaSuccess) return e;
         configured = true;
@@ -415,7 +505,13 @@ static cudaError_t launch_one(const GemvArgs& args, int grid, size_t smem, bool 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_fused_kernel<K, CB>, args);
+    return cudaLaunchKernelEx(&cfg, gemv_fused_kernel<K, CB, MULTI>, args);
+}
+
+template <int K, int CB>
+static cudaError_t launch_one(const GemvArgs& args, int grid, size_t smem, bool pdl, cudaStream_t stream) {
+    return args.call.rows == 1 ? launch_rows<K, CB, false>(args, grid, smem, pdl, stream)
+                               : launch_rows<K, CB, true>(args, grid, smem, pdl, stream);
 }
 
 template <int CB>
