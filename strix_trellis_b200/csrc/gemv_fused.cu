@@ -139,13 +139,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
 
     // Segment walk shared by decode and epilogue warps: the CTA's unit range is cut at
     // column-block ends (where a contribution is flushed) and at the staging capacity.
+    // Each warp calls it once per segment, in order; the position is carried, not divided out.
+    int walk_nb = mine.begin / hblocks, walk_hb0 = mine.begin - walk_nb * hblocks;
     auto segment = [&](int done, int& nb, int& hb0, int& len) {
-        const int u = mine.begin + done;
-        nb = u / hblocks;
-        hb0 = u - nb * hblocks;
+        nb = walk_nb;
+        hb0 = walk_hb0;
         len = my_units - done;
         if (len > hblocks - hb0) len = hblocks - hb0;
         if (len > args.act_blocks) len = args.act_blocks;
+        walk_hb0 += len;
+        if (walk_hb0 == hblocks) { walk_hb0 = 0; ++walk_nb; }
     };
 
     if (warp == kConsumers + 1) {
@@ -311,9 +314,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     // CTA's range touches is staged exactly once, at its own slot, before the loop starts.
     // The input scales of a warp's first block are weights (immutable): they are fetched
     // before the wait on the prior grid, so only the activation load follows it.
-    const bool resident = hblocks <= args.act_blocks;
+    const bool resident = MULTI ? hblocks <= args.act_blocks : true;  // the one-row kernel is only launched resident
     const int need = my_units < hblocks ? my_units : hblocks;
-    const int hb_first = mine.begin % hblocks;
+    const int hb_first = walk_hb0;
     uint16_t su_first[4] = {0, 0, 0, 0};
     if (resident && warp < rows * need) {
         int hb = hb_first + warp % need;
@@ -510,8 +513,9 @@ static cudaError_t launch_rows(const GemvArgs& args, int grid, size_t smem, bool
 
 template <int K, int CB>
 static cudaError_t launch_one(const GemvArgs& args, int grid, size_t smem, bool pdl, cudaStream_t stream) {
-    return args.call.rows == 1 ? launch_rows<K, CB, false>(args, grid, smem, pdl, stream)
-                               : launch_rows<K, CB, true>(args, grid, smem, pdl, stream);
+    const bool lean = args.call.rows == 1 && args.call.w.inputs / 128 <= args.act_blocks;
+    return lean ? launch_rows<K, CB, false>(args, grid, smem, pdl, stream)
+                : launch_rows<K, CB, true>(args, grid, smem, pdl, stream);
 }
 
 template <int CB>
