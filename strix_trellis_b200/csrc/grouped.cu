@@ -111,43 +111,21 @@ __global__ void __launch_bounds__(kThreadsG, 2) grouped_linear_kernel(const Grou
                 mbar_wait(full0 + 8 * (i % stages), (uint32_t)(i / stages) & 1, args.status, kTimeoutDrain);
         }
     } else {
-        // input stages of the gathered rows for this K partition, in B-fragment order; a warp
-        // keeps four (row, block) items in flight so that their global loads overlap
+        // input stages of the gathered rows for this K partition, in B-fragment order
         __half* act_h = reinterpret_cast<__half*>(act);
-        const int n_items = rows * nblk;
-        for (int base = warp; base < n_items; base += 4 * kWarps) {
-            float xv[4][4];
-            uint16_t sc[4][4];
+        for (int item = warp; item < rows * nblk; item += kWarps) {
+            const int r = item / nblk, blk = item % nblk;
+            const float* xr = pr.x + (long long)pr.x_row[r] * pr.x_stride + (size_t)(hb_begin + blk) * 128;
+            const uint16_t* su = w.suh + (size_t)(hb_begin + blk) * 128;
+            float v[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int item = base + u * kWarps;
-                if (item < n_items) {
-                    const int r = item / nblk, blk = item - r * nblk;
-                    const float* xr = pr.x + (long long)pr.x_row[r] * pr.x_stride + (size_t)(hb_begin + blk) * 128;
-                    const uint16_t* su = w.suh + (size_t)(hb_begin + blk) * 128;
+            for (int j = 0; j < 4; ++j) v[j] = __half2float(scale_input(xr[lane + 32 * j], su[lane + 32 * j]));
+            hadamard128_warp(v, lane);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        xv[u][j] = xr[lane + 32 * j];
-                        sc[u][j] = su[lane + 32 * j];
-                    }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int item = base + u * kWarps;
-                if (item < n_items) {
-                    const int r = item / nblk, blk = item - r * nblk;
-                    float v[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[j] = __half2float(scale_input(xv[u][j], sc[u][j]));
-                    hadamard128_warp(v, lane);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int e = lane + 32 * j, kt = e >> 4, kk = e & 15;
-                        const int q = (kk & 7) >> 1, hi = kk >> 3, lo = kk & 1;
-                        act_h[((((size_t)blk * rows + r) * 8 + kt) * 4 + q) * 4 + hi * 2 + lo] = __float2half_rn(v[j]);
-                    }
-                }
+            for (int j = 0; j < 4; ++j) {
+                const int e = lane + 32 * j, kt = e >> 4, kk = e & 15;
+                const int q = (kk & 7) >> 1, hi = kk >> 3, lo = kk & 1;
+                act_h[((((size_t)blk * rows + r) * 8 + kt) * 4 + q) * 4 + hi * 2 + lo] = __float2half_rn(v[j]);
             }
         }
         named_barrier(1, kWarps * 32);
