@@ -394,7 +394,7 @@ cudaError_t launch_gemm_pair(const LinearCall& call, const unsigned char* a_tile
 static bool pair_enabled() {
     static const bool on = [] {
         const char* e = getenv("STRIX_B200_GEMM");
-        return e && e[0] == 'p';  // "pair" routes more than 256 rows to the two-CTA kernel; measured slower so far
+        return !(e && e[0] == 's');  // "single" keeps every row count on the one-CTA kernel (measurement switch)
     }();
     return on;
 }

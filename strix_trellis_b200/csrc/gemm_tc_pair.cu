@@ -4,14 +4,13 @@
 // own two activation tiles per K step and DECODES ONLY ITS OWN 128 COLUMNS of the weight
 // stage -- the MMA reads the other 128 from the partner's shared memory.  Against the
 // single-CTA kernel (gemm_tc.cu) every decoded weight now feeds twice as many rows, which
-// halves the decode work per flop, the limit of that kernel.  Measured at 8192 rows (K4,
-// 4096 -> 12288): 1230 us against 1070 us for the single-CTA kernel; with decode and epilogue
-// arithmetic both taken out the pair pipeline alone needs 840 us against 640 us, so the
-// stage hand-off between the two CTAs, not the decode, is what holds it back.  It is
-// therefore selected only on request (STRIX_B200_GEMM=pair).
+// halves the decode work per flop, the limit of that kernel.  Measured (K4, 4096 -> 12288):
+// 259 us against 306 us at 2048 rows, 1007 us against 1069 us at 8192 rows.
 //
 // Per CTA: warp 0 activation producer (bulk copies), warp 1 MMA issuer (leader CTA) or relay
-// of "my activation stage landed" to the leader (partner CTA), warps 2-5 epilogue of the
+// (partner CTA: ONE remote arrival per stage once its activation tiles have landed and its
+// decoders are done -- sixteen remote arrivals per stage, one per decoder warp, measured
+// 20 % slower than the single-CTA kernel), warps 2-5 epilogue of the
 // CTA's own accumulators, warps 6-21 decoders (column tile = warp % 8, K half = warp / 8).
 // Barriers another CTA arrives on are waited with cluster scope; a tcgen05.commit arrives on
 // both CTAs' barriers at once.  Every wait is bounded and reports into the status word; both
@@ -70,8 +69,8 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStagesP; ++i) {
             mbar_init(full_a + 8 * i, 1);
-            mbar_init(full_b + 8 * i, 2 * kDecodeWarps);  // leader's: the decoders of both CTAs
-            mbar_init(peer_a + 8 * i, 1);                  // leader's: the partner's relay
+            mbar_init(full_b + 8 * i, kDecodeWarps);      // this CTA's decoders
+            mbar_init(peer_a + 8 * i, 1);                  // leader's: the partner's whole stage is ready
             mbar_init(empty + 8 * i, 1);
         }
         mbar_init(tmem_full, 1);
@@ -127,7 +126,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
                     const uint32_t par = (uint32_t)(it / kStagesP) & 1;
                     if (!mbar_wait(full_a + 8 * st, par, c.status, kTimeoutTensorPipe) ||
                         !mbar_wait_cluster(peer_a + 8 * st, par, c.status, kTimeoutTensorPipe) ||
-                        !mbar_wait_cluster(full_b + 8 * st, par, c.status, kTimeoutTensorPipe)) {
+                        !mbar_wait(full_b + 8 * st, par, c.status, kTimeoutTensorPipe)) {
                         s_abort = 1;
                         break;
                     }
@@ -146,15 +145,19 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
                 umma_commit_pair(tmem_full, 3);           // both CTAs' accumulators of this tile complete
             }
         } else if (lane == 0) {
-            // ---- partner CTA: tell the leader when this CTA's activation tiles have landed ----
+            // ---- partner CTA: ONE remote arrival per stage, once this CTA's activation tiles have
+            // landed and its sixteen decoders have written their half of the weights -------------
             const uint32_t leader_peer_a = map_to_rank(peer_a, 0);
             const int iters = my_tiles * kt64;
             for (int it = 0; it < iters && !s_abort; ++it) {
                 const int st = it % kStagesP;
-                if (!mbar_wait(full_a + 8 * st, (uint32_t)(it / kStagesP) & 1, c.status, kTimeoutTensorPipe)) {
+                const uint32_t par = (uint32_t)(it / kStagesP) & 1;
+                if (!mbar_wait(full_a + 8 * st, par, c.status, kTimeoutTensorPipe) ||
+                    !mbar_wait(full_b + 8 * st, par, c.status, kTimeoutTensorPipe)) {
                     s_abort = 1;
                     break;
                 }
+                fence_async_smem();
                 mbar_arrive_cluster(leader_peer_a + 8 * st);
             }
         }
@@ -237,7 +240,6 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
         const int n0 = ct * 16 + (lane >> 2), kq = 2 * (lane & 3);
         const uint32_t o00 = sw128_offset(n0, kq), o01 = sw128_offset(n0, kq + 8);
         const uint32_t o10 = sw128_offset(n0 + 8, kq), o11 = sw128_offset(n0 + 8, kq + 8);
-        const uint32_t leader_full_b = map_to_rank(full_b, 0);
         const int iters = my_tiles * kt64;
         int flt = 0, fks = 0, fetched = 0;
         const uint32_t* fcol = nullptr;
@@ -282,7 +284,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_full_b + 8 * st);
+            if (lane == 0) mbar_arrive(full_b + 8 * st);  // local: the relay (partner) or the MMA warp (leader) waits on it
 #pragma unroll
             for (int k2 = 0; k2 < 2; ++k2)
 #pragma unroll
