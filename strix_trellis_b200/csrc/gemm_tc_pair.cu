@@ -7,6 +7,11 @@
 // halves the decode work per flop, the limit of that kernel.  Measured (K4, 4096 -> 12288):
 // 259 us against 306 us at 2048 rows, 1007 us against 1069 us at 8192 rows.
 //
+// A variant with ONE accumulator per CTA (256-row pair tile), which leaves half of tensor memory
+// free so that the epilogue of a tile overlaps the next tile's main loop, measured slower
+// (1337 us against 1007 us at 8192 rows): each decoded weight then feeds 256 rows instead of
+// 512 and the decoders, not the epilogue, set the pace again.
+//
 // Per CTA: warp 0 activation producer (bulk copies), warp 1 MMA issuer (leader CTA) or relay
 // (partner CTA: ONE remote arrival per stage once its activation tiles have landed and its
 // decoders are done -- sixteen remote arrivals per stage, one per decoder warp, measured
