@@ -59,10 +59,14 @@ def all_reduce_rows(local, group=None):
     return local
 
 
+_COLUMN_INDEX = {}
+
+
 def all_gather_columns(local, widths, group=None):
     """Column-parallel recombination: rank r's [rows, widths[r]] block lands at its column
     offset of the [rows, sum(widths)] result.  Shards may be uneven (e.g. 1010 H128 blocks
-    over 4 or 8 ranks): every rank pads to the widest shard for the collective."""
+    over 4 or 8 ranks): every rank pads to the widest shard for the collective, and one
+    gather with a cached column index drops the padding afterwards."""
     import torch
     import torch.distributed as dist
     world = len(widths)
@@ -70,5 +74,12 @@ def all_gather_columns(local, widths, group=None):
     padded = local if local.shape[1] == wmax else torch.nn.functional.pad(local, (0, wmax - local.shape[1]))
     gathered = torch.empty((world * rows, wmax), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(gathered, padded.contiguous(), group=group)
-    gathered = gathered.view(world, rows, wmax)
-    return torch.cat([gathered[r, :, :widths[r]] for r in range(world)], dim=1)
+    by_row = gathered.view(world, rows, wmax).permute(1, 0, 2).reshape(rows, world * wmax)
+    if min(widths) == wmax:
+        return by_row
+    key = (tuple(widths), str(local.device))
+    index = _COLUMN_INDEX.get(key)
+    if index is None:
+        index = torch.cat([torch.arange(r * wmax, r * wmax + widths[r]) for r in range(world)]).to(local.device)
+        _COLUMN_INDEX[key] = index
+    return by_row.index_select(1, index)
