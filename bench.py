@@ -473,31 +473,53 @@ def run_gpu(args):
 
     # ---- end to end: host activations in, host outputs out ---------------------------------
     # The step's 96 activation rows sit in ONE pinned host buffer and its 96 output rows return
-    # to ONE pinned host buffer: [copy in, 96 x strix_linear_plan_submit, copy out] is the timed
-    # unit (captured once, replayed), every call reading its own slice and writing its own.
+    # to ONE pinned host buffer: [copies in, 96 x strix_linear_plan_submit, copies out] is the
+    # timed unit (captured once, replayed), every call reading its own slice and writing its own.
     e2e_steps = max(1, min(args.steps, 10))
     n_in = sum(len(g["weights"]) * g["layer"].inputs for g in groups) * ROWS
     n_out = sum(len(g["weights"]) * g["layer"].outputs for g in groups) * ROWS
     hx_all, hy_all = torch.empty(n_in).pin_memory(), torch.empty(n_out).pin_memory()
     dx_all = torch.empty(n_in, dtype=torch.float32, device="cuda")
     dy_all = torch.empty(n_out, dtype=torch.float32, device="cuda")
-    e2e_plans, oi, oo = [], 0, 0
+    e2e_plans, spans, oi, oo = [], [], 0, 0  # spans: per shape (plans, input slice, output slice)
     with torch.cuda.stream(stream):
         for g in groups:
             i_n, o_n = g["layer"].inputs * ROWS, g["layer"].outputs * ROWS
+            i0, o0, first = oi, oo, len(e2e_plans)
             for w in g["weights"]:
                 hx_all[oi:oi + i_n] = g["hx"].reshape(-1)
                 e2e_plans.append(w.plan(dx_all[oi:oi + i_n].view(ROWS, -1), dy_all[oo:oo + o_n].view(ROWS, -1),
                                         N.OP_GEMV, stream=stream))
                 oi, oo = oi + i_n, oo + o_n
+            spans.append((e2e_plans[first:], slice(i0, oi), slice(o0, oo)))
     h2d, d2h = n_in * 4, n_out * 4
+    # Copies are pipelined by shape on a second stream (fork / join inside the capture): the
+    # rows of shape k+1 come in and the rows of shape k-1 go out while shape k computes.
+    copy_stream = torch.cuda.Stream()
     e2e_graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):
         with torch.cuda.graph(e2e_graph, stream=stream):
-            dx_all.copy_(hx_all, non_blocking=True)
-            for p in e2e_plans:
-                p.submit()
-            hy_all.copy_(dy_all, non_blocking=True)
+            ready = []
+            copy_stream.wait_stream(stream)  # fork
+            with torch.cuda.stream(copy_stream):
+                for _, xs, _ in spans:
+                    dx_all[xs].copy_(hx_all[xs], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(copy_stream)
+                    ready.append(ev)
+            done = []
+            for (plans, _, _), ev in zip(spans, ready):
+                stream.wait_event(ev)
+                for p in plans:
+                    p.submit()
+                ev2 = torch.cuda.Event()
+                ev2.record(stream)
+                done.append(ev2)
+            with torch.cuda.stream(copy_stream):
+                for (_, _, ys), ev2 in zip(spans, done):
+                    copy_stream.wait_event(ev2)
+                    hy_all[ys].copy_(dy_all[ys], non_blocking=True)
+            stream.wait_stream(copy_stream)  # join
         for _ in range(3):
             e2e_graph.replay()
         barrier()
