@@ -565,6 +565,11 @@ def run_gpu(args):
                 v["frac_of_measured_dense_peak"] = round(v["TFLOPs"] / gemm_peak, 3)
             extra["gemv_4096x14336_rates_rows"] = gemv_sweep(torch, ctx, stream)
             extra["prefill_gemm_K4_4096x12288"] = gemm
+            for bits in (5, 6):
+                other = gemm_case(torch, ctx, stream, [2048, 8192], bits=bits)
+                for v in other.values():
+                    v["frac_of_measured_dense_peak"] = round(v["TFLOPs"] / gemm_peak, 3)
+                extra[f"prefill_gemm_K{bits}_4096x12288"] = other
             extra["moe_bank32_top8_K2_one_rank"] = moe_case(torch, ctx, stream, [1, 8, 64])
         if world > 1:
             dist.barrier()
