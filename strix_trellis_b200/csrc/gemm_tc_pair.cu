@@ -30,10 +30,10 @@ namespace st {
 
 namespace {
 constexpr int kBM = 128, kMT = 2, kBN = 256, kBK = 64;
-constexpr int kStagesP = 4;
+constexpr int kStagesP = 3;
 constexpr int kTileBytes = kBM * kBK * 2;               // 16 KB: 128 rows x 64 binary16
 constexpr int kStageBytesP = (kMT + 1) * kTileBytes;    // A0, A1, this CTA's half of B
-constexpr int kDecodeWarps = 16, kEpiWarps = 4;
+constexpr int kDecodeWarps = 16, kEpiWarps = 8;  // two epilogue warps per tensor-memory lane quarter
 constexpr int kThreadsP = (2 + kEpiWarps + kDecodeWarps) * 32;
 constexpr int kStagingStride = 129;
 constexpr int kStagingBytes = 16 * kStagingStride * 4;
@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
             }
             tc_fence_after_sync();
             for (int mt = 0; mt < kMT; ++mt) {
-                for (int cb = 0; cb < kBN / 128; ++cb) {
+                for (int cb = (warp - 2) >> 2; cb < kBN / 128; cb += kEpiWarps / 4) {  // this warp's column block(s)
                     const int nb = np * (kBN / 128) + cb;
                     if (nb >= nblocks) continue;  // odd column-block count: second half is padding
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + mt * kBN + cb * 128;
