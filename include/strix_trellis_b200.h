@@ -72,6 +72,20 @@ strix_status strix_b200_device_status(strix_context context, uint32_t *out_bits)
  * or writes anything.  No counterpart in the reference. */
 strix_status strix_b200_set_programmatic_launch(strix_context context, uint32_t enabled);
 
+/* Routed-expert combine at a token's home rank, for callers that run the expert projections
+ * elsewhere (expert parallelism): y[t] = alpha * sum over slots s ascending, from +0, of
+ * RN32(scores[t,s] * rows[t,s,:]) + beta * y[t]; a score of exactly zero skips its slot
+ * (the combine of strix_tp_moe_plan_submit, reference src/tp_moe.hip:112-164, on its own).
+ * rows: F32 [tokens, top_k, width] contiguous, scores: F32 [tokens, top_k], y: F32 rows
+ * y_stride elements apart; all device memory of the context's device.  beta == 0 never
+ * reads y.  While `stream` is being captured into a graph the pointers are not inspected
+ * (the driver queries that do it would invalidate the capture).  No counterpart as a
+ * separate entry point in the reference. */
+strix_status strix_b200_moe_combine(strix_context context, const float *rows, const float *scores,
+                                    uint32_t tokens, uint32_t top_k, uint32_t width, float *y,
+                                    uint64_t y_stride, float alpha, float beta,
+                                    const strix_stream *stream);
+
 /* strix_gemv for callers that may not allocate.  It has no counterpart in the reference.
  *
  * Some engines hand every byte of device memory to their own arena when they start and

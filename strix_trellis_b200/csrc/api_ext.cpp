@@ -1,6 +1,7 @@
 // Entry points declared in strix_trellis_b200.h: stage probes and runtime switches.
 #include "api_internal.h"
 #include "gemv_partition.h"
+#include "grouped.h"
 
 using namespace sapi;
 
@@ -80,6 +81,45 @@ strix_status strix_b200_gemv_splits(strix_context c, strix_weights w, uint32_t r
     if (!c || !w || w->owner != c || rows < 1 || rows > 8) return STRIX_ERROR_INVALID_ARGUMENT;
     *out = (uint32_t)st::plan_gemv(w->device, (int)rows, c->sm_count).splits;
     return STRIX_SUCCESS;
+}
+
+strix_status strix_b200_moe_combine(strix_context c, const float* rows, const float* scores, uint32_t tokens,
+                                    uint32_t top_k, uint32_t width, float* y, uint64_t y_stride, float alpha,
+                                    float beta, const strix_stream* stream) {
+    strix_status s = context_check(c);
+    if (s != STRIX_SUCCESS) return s;
+    // Stream and pointer provenance are inspected with runtime / driver queries, which a
+    // capturing stream does not tolerate: while `stream` is being captured into a graph only
+    // the arithmetic checks apply.
+    cudaStream_t cs = stream ? reinterpret_cast<cudaStream_t>(stream->hip_stream) : nullptr;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cs && cudaStreamIsCapturing(cs, &capturing) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    }
+    if (capturing == cudaStreamCaptureStatusNone) {
+        s = stream_check(c, stream, cs);
+        if (s != STRIX_SUCCESS) return s;
+    } else if (stream->struct_size != sizeof(strix_stream) || stream->abi_version != STRIX_TRELLIS_ABI_VERSION) {
+        return STRIX_ERROR_ABI_MISMATCH;
+    }
+    if (!std::isfinite(alpha) || !std::isfinite(beta) || top_k < 1 || top_k > STRIX_B200_MOE_MAX_TOP_K ||
+        width < 1 || tokens > STRIX_B200_MOE_MAX_ROWS || y_stride < width)
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    if (!tokens) return STRIX_SUCCESS;
+    const uint64_t n_rows = (uint64_t)tokens * top_k * width * 4, n_scores = (uint64_t)tokens * top_k * 4;
+    const uint64_t n_y = ((uint64_t)(tokens - 1) * y_stride + width) * 4;
+    if (overlap(rows, n_rows, y, n_y) || overlap(scores, n_scores, y, n_y)) return STRIX_ERROR_INVALID_ARGUMENT;
+    if (capturing == cudaStreamCaptureStatusNone) {
+        s = device_buffer(c, rows, n_rows, 4);
+        if (s == STRIX_SUCCESS) s = device_buffer(c, scores, n_scores, 4);
+        if (s == STRIX_SUCCESS) s = device_buffer(c, y, n_y, 4);
+        if (s != STRIX_SUCCESS) return s;
+    } else if (!rows || !scores || !y) {
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    }
+    return cuda_status(st::launch_moe_combine(rows, scores, nullptr, (int)tokens, (int)top_k, (int)width, y,
+                                              (long long)y_stride, alpha, beta, cs));
 }
 
 // Pure host arithmetic: no context, no device.

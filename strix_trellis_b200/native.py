@@ -198,6 +198,7 @@ PROTOTYPES = {
     "strix_b200_core_exact": (C.c_int, [vp, vp, vp, u32, vp, P(Stream)]),
     "strix_b200_gemv_splits": (C.c_int, [vp, vp, u32, P(u32)]),
     "strix_b200_gemv_partition": (C.c_int, [u64, u64, u32, u32, u64, P(u64)]),
+    "strix_b200_moe_combine": (C.c_int, [vp, vp, vp, u32, u32, u32, vp, u64, f32, f32, P(Stream)]),
     "strix_b200_device_status": (C.c_int, [vp, P(u32)]),
     "strix_b200_set_programmatic_launch": (C.c_int, [vp, u32]),
     "strix_b200_gemv_noalloc": (C.c_int, [vp, P(MatmulDesc), P(Stream)]),

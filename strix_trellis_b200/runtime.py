@@ -49,6 +49,16 @@ class Context:
     def prepare(self, layer, stream=None, use_blob=False):
         return Weights(self, layer, stream, use_blob)
 
+    def moe_combine(self, rows, scores, y, alpha=1.0, beta=0.0, stream=None):
+        """y[t] = alpha * sum_s (ascending, from +0) scores[t,s] * rows[t,s,:] + beta * y[t];
+        rows [T, top_k, width] and scores [T, top_k] contiguous float32 CUDA tensors."""
+        tokens, top_k, width = rows.shape
+        sd = _cur_stream(stream)
+        N.check(self.lib.strix_b200_moe_combine(self.handle, rows.data_ptr(), scores.data_ptr(), tokens, top_k, width,
+                                                y.data_ptr(), y.stride(0), alpha, beta, C.byref(sd)),
+                "strix_b200_moe_combine")
+        return y
+
 
 def _bytes_view(a, dtype):
     a = np.ascontiguousarray(np.asarray(a), dtype=dtype)

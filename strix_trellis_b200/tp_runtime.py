@@ -153,12 +153,10 @@ class ExpertParallelMoE:
             dist.all_to_all_single(self.back, self.out_rows, group=self.group)
         each = torch.empty((count, self.model), dtype=torch.float32, device="cuda")
         each[order] = self.back[slot]
-        each = each.view(tokens, top_k, self.model)
-        y = torch.zeros((tokens, self.model), dtype=torch.float32, device="cuda")
-        for s in range(top_k):  # ascending slot order; mul and add round separately
-            term = scores[:, s:s + 1] * each[:, s]
-            y = torch.where(scores[:, s:s + 1] == 0, y, y + term)
-        return y * alpha if alpha != 1.0 else y
+        y = torch.empty((tokens, self.model), dtype=torch.float32, device="cuda")
+        if tokens:  # ascending slot order from +0, a zero score skips its slot: the plan's own combine
+            self.ctx.moe_combine(each.view(tokens, top_k, self.model), scores.contiguous(), y, alpha=alpha)
+        return y
 
     def capture(self, tokens):
         """Freezes forward() for `tokens` home tokens into a CUDA graph over static input

@@ -159,6 +159,33 @@ def test_moe_full_expert_size(ctx):
             w.close()
 
 
+def test_standalone_combine_is_the_plan_combine(ctx):
+    """strix_b200_moe_combine: ascending slot order from +0 with separately rounded products, a
+    zero score skips its slot (even over a NaN row), alpha/beta as in the plans -- bit for bit
+    against the same arithmetic in NumPy float32."""
+    rng = synthetic.rng_for(8100)
+    tokens, top_k, width = 5, 6, 384
+    rows = rng.normal(0, 3, (tokens, top_k, width)).astype(np.float32)
+    scores = rng.uniform(0, 1, (tokens, top_k)).astype(np.float32)
+    scores[1, 2] = 0.0
+    rows[1, 2] = np.nan  # a skipped slot is never read into the sum
+    old = rng.normal(0, 1, (tokens, width)).astype(np.float32)
+    want = np.zeros((tokens, width), np.float32)
+    for s in range(top_k):
+        term = (scores[:, s:s + 1] * rows[:, s]).astype(np.float32)
+        want = np.where(scores[:, s:s + 1] == 0, want, (want + term).astype(np.float32))
+    want = (np.float32(-0.5) * want).astype(np.float32) + (np.float32(0.25) * old).astype(np.float32)
+    ybuf = torch.zeros((tokens, width + 128), device="cuda")
+    y = ybuf[:, :width]
+    y.copy_(dev(old))
+    ctx.moe_combine(dev(rows), dev(scores), y, alpha=-0.5, beta=0.25)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host(y), want.astype(np.float32))
+    assert (host(ybuf[:, width:]) == 0).all()
+    with pytest.raises(N.StrixError):
+        ctx.moe_combine(dev(rows), dev(scores), dev(rows).view(tokens, -1)[:, :width])  # output aliases the rows
+
+
 def test_moe_rejections(ctx):
     import ctypes as C
     from strix_trellis_b200.runtime import MoePlan
