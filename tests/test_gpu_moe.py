@@ -182,8 +182,9 @@ def test_standalone_combine_is_the_plan_combine(ctx):
     torch.cuda.synchronize()
     np.testing.assert_array_equal(host(y), want.astype(np.float32))
     assert (host(ybuf[:, width:]) == 0).all()
+    rows_d = dev(rows)
     with pytest.raises(N.StrixError):
-        ctx.moe_combine(dev(rows), dev(scores), dev(rows).view(tokens, -1)[:, :width])  # output aliases the rows
+        ctx.moe_combine(rows_d, dev(scores), rows_d.view(tokens, -1)[:, :width])  # output aliases the rows
 
 
 def test_moe_rejections(ctx):
