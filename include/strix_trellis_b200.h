@@ -92,7 +92,7 @@ strix_status strix_b200_moe_combine(strix_context context, const float *rows, co
  * never call the CUDA allocator again: a cudaMalloc in the middle of a decode loop
  * serialises the whole device, and with the arena holding everything it would simply
  * fail.  Such a caller has nowhere to take the GEMV's split-K scratch from.  This entry
- * point needs none: its arrival counters and partial planes sit in a fixed array of
+ * point needs none: its partial planes sit in a fixed array of
  * STRIX_B200_NOALLOC_SCRATCH_BYTES inside the library image (every GPU that loads the
  * library holds that array until the process exits).  It calls no allocating routine.
  *

@@ -24,7 +24,7 @@ struct strix_weights_impl {
     void* allocation = nullptr;
     size_t allocation_bytes = 0;
     size_t plan_refs = 0;
-    // Scratch that plans created on these weights own (arrival counters, partial
+    // Scratch that plans created on these weights own (partial
     // planes).  A captured graph may replay after its plan is destroyed but not after
     // the weights are, so the scratch lives until the weights are destroyed
     // (the reference keeps its completion counters the same way, src/api.hip:24-27).
@@ -85,7 +85,7 @@ st::LinearCall make_call(strix_context c, const strix_matmul_desc& d, const View
 
 // Scratch requirement of one linear with `rows` rows through the public entry points.
 uint64_t linear_workspace(strix_context c, const st::DeviceWeights& w, int rows);
-// Enqueue a validated linear.  `zero_counters`: clear arrival counters first (needed
+// Enqueue a validated linear.  `zero_counters`: mark the fold scratch empty first (needed
 // when the workspace content is unknown, i.e. outside prepared plans).
 cudaError_t enqueue_linear(strix_context c, const st::LinearCall& call, void* workspace,
                            bool zero_counters, cudaStream_t stream);

@@ -65,7 +65,7 @@ struct GemvPlan {
     int stages;          // shared-memory ring depth
     int act_blocks;      // H128 blocks of core input staged at a time
     size_t smem_bytes;
-    size_t counter_bytes;   // arrival counters [N/128] at the start of the workspace
+    size_t counter_bytes;   // reserved area at the start of the workspace (0: the fold needs no counters)
     size_t partial_bytes;   // float [grid][2][rows][128] after the counters
 };
 GemvPlan plan_gemv(const DeviceWeights& w, int rows, int sm_count);

@@ -155,8 +155,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
         // ---- epilogue warp: turns dumped accumulators into partial planes or outputs ------
         // Everything a flush needs that does not depend on the accumulators (contributor
         // range, output scales, bias) is resolved BEFORE the wait for the dump, while the
-        // decode warps are still busy; after the dump the critical path is one plane write,
-        // one release/acquire atomic and, for the last arriver, one batch of plane loads.
+        // decode warps are still busy; after the dump the critical path is one plane write for
+        // a contributor and, for the folding CTA, the wait for the others' plane words.
         pdl_wait_prior_grid();  // y and scratch may belong to the prior grid
         int done = 0, flush = 0;
         while (done < my_units) {
