@@ -62,7 +62,9 @@ strix_status strix_b200_gemv_partition(uint64_t inputs, uint64_t outputs, uint32
 
 /* Reads and clears the context's device status word.  Non-zero means that a bounded
  * wait inside a kernel gave up (bit 0 weight ring full-wait, bit 1 empty-wait, bit 2
- * drain at exit, bit 3 tensor pipeline, bit 4 split-K fold); results of that launch are invalid.
+ * drain at exit, bit 3 tensor pipeline, bit 4 split-K fold); results of that launch are invalid,
+ * and after bit 4 the plan whose launch it was should be recreated (its fold scratch may hold
+ * words of the abandoned launch; direct strix_gemv calls reset their scratch on every call).
  * Synchronises the device.  No counterpart in the reference (its kernels never wait). */
 strix_status strix_b200_device_status(strix_context context, uint32_t *out_bits);
 
