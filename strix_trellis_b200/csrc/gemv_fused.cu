@@ -68,6 +68,62 @@ __host__ __device__ inline int stage_bytes(int bits) { return 2048 * bits; }
 
 }  // namespace
 
+// One output row of one column block, by one warp: this CTA's own contribution (`own`, the
+// two k-group planes of the shared-memory fold buffer) first, then the planes of CTAs
+// first+1 .. last in ascending K order, each polled word by word until it is no longer empty
+// (bounded) and marked empty again; then output H128, svh, bias, alpha, beta.
+__device__ __forceinline__ void fold_row(const GemvArgs& args, const float* own, int r, int rows, int nb, int first,
+                                         int last, int lane, const float (&sv)[4], const float (&bs)[4]) {
+    const LinearCall& c = args.call;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        v[j] = __fadd_rn(0.f, __fadd_rn(own[r * 128 + lane + 32 * j], own[1024 + r * 128 + lane + 32 * j]));
+    for (int p0 = first + 1; p0 <= last; p0 += 8) {  // eight planes in flight
+        uint32_t t[8][4];
+        bool have = false;
+        for (uint32_t tries = 0; tries < (1u << 18) && !have; ++tries) {
+            bool all = true;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const uint32_t* src =
+                    reinterpret_cast<const uint32_t*>(args.partials) + ((size_t)(p0 + q) * rows + r) * 128 + lane;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    t[q][j] = p0 + q <= last ? ld_relaxed_gpu(src + 32 * j) : 0u;
+                    all = all && t[q][j] != kEmptyWord;
+                }
+            }
+            have = __all_sync(0xFFFFFFFFu, all);
+        }
+        if (!have) {  // bounded: report and leave this row unwritten
+            if (lane == 0) atomicOr(c.status, kTimeoutFold);
+            return;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            if (p0 + q <= last) {
+                uint32_t* src = reinterpret_cast<uint32_t*>(args.partials) + ((size_t)(p0 + q) * rows + r) * 128 + lane;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    v[j] = __fadd_rn(v[j], __uint_as_float(t[q][j]));
+                    st_relaxed_gpu(src + 32 * j, kEmptyWord);  // empty again for the next launch
+                }
+            }
+        }
+    }
+    hadamard128_warp(v, lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float* out = c.y + (long long)r * c.y_stride + nb * 128 + lane + 32 * j;
+        float value = __fmul_rn(v[j], sv[j]);
+        if (c.w.bias) value = __fadd_rn(value, bs[j]);
+        value = __fmul_rn(value, c.alpha);
+        if (c.beta != 0.0f) value = __fadd_rn(value, __fmul_rn(c.beta, *out));
+        *out = value;
+    }
+}
+
 // MULTI selects the code for more than one activation row (several staging items per warp in
 // flight, fold sums in shared memory); the one-row instantiation carries none of it, which
 // keeps the latency-critical head and tail of the decode case as short as they can be.
@@ -188,117 +244,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
                     st_relaxed_gpu(plane + e, __float_as_uint(__fadd_rn(f0[e], f0[1024 + e])));
                 stamp(1);
             } else {
-                // This CTA holds the FIRST K range of the block, which is the end of its own unit
-                // range: every other contributor finishes at about the same time or earlier.  It
-                // folds in ascending K order from +0: its own contribution (still in shared
-                // memory), then the others' planes.  The sums are kept in shared memory (each lane
-                // only ever touches its own words) and the (row, plane) pairs are polled eight at a
-                // time, plane index fastest, so several rows share one round trip to L2.
-                float* accum = fold_base + buf * 2048;
-                const int planes = last - first, items = rows * planes;
-                bool folded = true;
-                if (!MULTI) {
-                    // one row: the sums stay in registers (the shortest tail for the decode case)
-                    float v[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        v[j] = __fadd_rn(0.f, __fadd_rn(f0[lane + 32 * j], f0[1024 + lane + 32 * j]));
-                    for (int p0 = first + 1; p0 <= last && folded; p0 += 8) {
-                        uint32_t t[8][4];
-                        bool have = false;
-                        for (uint32_t tries = 0; tries < (1u << 18) && !have; ++tries) {
-                            bool all = true;
-#pragma unroll
-                            for (int q = 0; q < 8; ++q) {
-                                const uint32_t* src =
-                                    reinterpret_cast<const uint32_t*>(args.partials) + (size_t)(p0 + q) * 128 + lane;
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    t[q][j] = p0 + q <= last ? ld_relaxed_gpu(src + 32 * j) : 0u;
-                                    all = all && t[q][j] != kEmptyWord;
-                                }
-                            }
-                            have = __all_sync(0xFFFFFFFFu, all);
-                        }
-                        if (!have) {
-                            if (lane == 0) atomicOr(c.status, kTimeoutFold);
-                            folded = false;
-                            break;
-                        }
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            if (p0 + q <= last) {
-                                uint32_t* src = reinterpret_cast<uint32_t*>(args.partials) + (size_t)(p0 + q) * 128 + lane;
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    v[j] = __fadd_rn(v[j], __uint_as_float(t[q][j]));
-                                    st_relaxed_gpu(src + 32 * j, kEmptyWord);
-                                }
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) accum[lane + 32 * j] = v[j];
-                } else {
-                for (int e = lane; e < rows * 128; e += 32)
-                    accum[e] = __fadd_rn(0.f, __fadd_rn(accum[e], accum[1024 + e]));
-                int next_row = 0, next_plane = 0;  // the pair after the ones batched so far (no divisions)
-                for (int i0 = 0; i0 < items && folded; i0 += 8) {
-                    uint32_t* src[8];
-                    int row_of[8];
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        row_of[q] = next_row;
-                        src[q] = reinterpret_cast<uint32_t*>(args.partials) +
-                                 ((size_t)(first + 1 + next_plane) * rows + next_row) * 128 + lane;
-                        if (i0 + q + 1 < items && ++next_plane == planes) { next_plane = 0; ++next_row; }
-                    }
-                    uint32_t t[8][4];
-                    bool have = false;
-                    for (uint32_t tries = 0; tries < (1u << 18) && !have; ++tries) {
-                        bool all = true;
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                t[q][j] = i0 + q < items ? ld_relaxed_gpu(src[q] + 32 * j) : 0u;
-                                all = all && t[q][j] != kEmptyWord;
-                            }
-                        }
-                        have = __all_sync(0xFFFFFFFFu, all);
-                    }
-                    if (!have) {  // bounded: report and leave this block unwritten
-                        if (lane == 0) atomicOr(c.status, kTimeoutFold);
-                        folded = false;
-                        break;
-                    }
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        if (i0 + q < items) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                float* a = accum + row_of[q] * 128 + lane + 32 * j;
-                                *a = __fadd_rn(*a, __uint_as_float(t[q][j]));
-                                st_relaxed_gpu(src[q] + 32 * j, kEmptyWord);  // empty again for the next launch
-                            }
-                        }
-                    }
-                }
-                }
-                for (int r = 0; r < rows && folded; ++r) {
-                    float v[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[j] = accum[r * 128 + lane + 32 * j];
-                    hadamard128_warp(v, lane);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float* out = c.y + (long long)r * c.y_stride + nb * 128 + lane + 32 * j;
-                        float value = __fmul_rn(v[j], sv[j]);
-                        if (c.w.bias) value = __fadd_rn(value, bs[j]);
-                        value = __fmul_rn(value, c.alpha);
-                        if (c.beta != 0.0f) value = __fadd_rn(value, __fmul_rn(c.beta, *out));
-                        *out = value;
-                    }
+                // The block is finished here: it lies inside this CTA's range, or this CTA holds
+                // its FIRST K range -- the end of its own unit range, so every other contributor
+                // finishes at about the same time or earlier.  With several rows and planes to
+                // wait for, the decode warps (idle by then) fold one row each instead.
+                if (!(MULTI && !whole)) {
+                    for (int r = 0; r < rows; ++r) fold_row(args, f0, r, rows, nb, first, last, lane, sv, bs);
                 }
             }
             // hand the buffer back (decode warps wait on this before its next reuse)
@@ -391,7 +342,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
 
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     bool ok = true;
-    int done = 0, flush = 0;
+    int done = 0, flush = 0, final_nb = 0;
     int next = kgroup;  // the unit (relative to the range) this warp decodes next
     int slot = kgroup % stages;
     uint32_t use = (uint32_t)(kgroup / stages) & 1;
@@ -455,6 +406,33 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
         }
         asm volatile("bar.arrive %0, %1;" ::"r"(2 + buf), "r"(kDumpThreads) : "memory");
         ++flush;
+        final_nb = nb;
+    }
+
+    // ---- several rows: the decode warps finish the CTA's last, shared column block ----------
+    // If this CTA folds that block (it holds the block's first K range, other CTAs hold the
+    // rest), warp r folds row r -- eight rows wait for their planes side by side instead of one
+    // after the other in the epilogue warp.  Every decode warp reaches the barrier, whatever
+    // its own waits returned, so it cannot be left short of arrivals.
+    if (MULTI && my_units > 0) {
+        const int blk_lo = final_nb * hblocks, blk_hi = blk_lo + hblocks;
+        if (!(mine.begin <= blk_lo && mine.end >= blk_hi)) {
+            int first, last;
+            contributors(args.split, blk_lo, blk_hi, first, last);
+            if (cta == first) {
+                named_barrier(1, kConsumers * 32);  // every decode warp has dumped its accumulators
+                if (ok && warp < rows) {
+                    float sv[4], bs[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int cidx = final_nb * 128 + lane + 32 * j;
+                        sv[j] = half_bits_to_float(c.w.svh[cidx]);
+                        bs[j] = c.w.bias ? c.w.bias[cidx] : 0.0f;
+                    }
+                    fold_row(args, fold_base + ((flush - 1) & 1) * 2048, warp, rows, final_nb, first, last, lane, sv, bs);
+                }
+            }
+        }
     }
 }
 
