@@ -4,6 +4,7 @@
 // (grouped GEMV).  The reference's creators differ only in the gfx1151 schedule they
 // pick; here they all run the fused GEMV kernel and differ only in who owns scratch.
 #include "api_internal.h"
+#include "grouped.h"
 
 using namespace sapi;
 
@@ -13,6 +14,11 @@ struct strix_tp_dense_plan_impl {
     std::vector<st::LinearCall> calls;
     std::vector<void*> scratch;  // per call; owned by the caller or by the weights
     cudaStream_t stream;
+    // grouped strided GEMV: every group is one problem of ONE grouped launch
+    st::GroupedProblem* problems = nullptr;  // device table inside the caller's workspace
+    int problem_count = 0;
+    st::GroupedPlan grouped{};
+    int inputs = 0, outputs = 0, codebook = 0;
 };
 
 namespace {
@@ -21,6 +27,9 @@ strix_status submit_plan(strix_tp_dense_plan_impl* p) {
     if (!p) return STRIX_ERROR_INVALID_ARGUMENT;
     const strix_status s = context_check(p->owner);
     if (s != STRIX_SUCCESS) return s;
+    if (p->problem_count)
+        return cuda_status(st::launch_grouped(p->problems, p->problem_count, p->inputs, p->outputs, p->codebook,
+                                              p->grouped, p->owner->status, p->owner->programmatic_launch, p->stream));
     for (size_t i = 0; i < p->calls.size(); ++i) {
         const cudaError_t e = enqueue_linear(p->owner, p->calls[i], p->scratch[i], false, p->stream);
         if (e != cudaSuccess) return cuda_status(e);
@@ -325,8 +334,12 @@ static strix_status grouped_views(strix_context c, const strix_grouped_gemv_desc
         m.push_back(one);
         v.push_back(view);
         offsets.push_back(total);
-        total += st::align_up(linear_workspace(c, w->device, view.rows));
     }
+    // one grouped launch: [problem table][per group: arrival counters, partial planes]
+    const st::DeviceWeights& w0 = d->weights[0]->device;
+    const st::GroupedPlan gp = st::plan_grouped(w0.inputs, w0.outputs, w0.bits, (int)d->group_count, c->sm_count);
+    total = st::align_up(d->group_count * sizeof(st::GroupedProblem)) +
+            d->group_count * (gp.counter_bytes_per_problem + gp.partial_bytes_per_problem);
     return STRIX_SUCCESS;
 }
 
@@ -355,20 +368,43 @@ strix_status strix_grouped_gemv_plan_create(strix_context c, const strix_grouped
     s = grouped_views(c, d, m, v, off, total);
     if (s != STRIX_SUCCESS) return s;
     for (size_t g = 0; g < m.size(); ++g) {
-        s = storage_check(c, m[g], v[g], (g || !d->workspace) ? 0 : total, d->workspace, d->workspace_bytes);
+        s = storage_check(c, m[g], v[g], g ? 0 : total, d->workspace, d->workspace_bytes);
         if (s != STRIX_SUCCESS) return s;
     }
     strix_tp_dense_plan_impl* p = new (std::nothrow) strix_tp_dense_plan_impl{};
     if (!p) return STRIX_ERROR_OUT_OF_MEMORY;
     p->owner = c;
     p->stream = cs;
-    for (size_t g = 0; g < m.size() && s == STRIX_SUCCESS; ++g) {
-        void* scratch = nullptr;
-        s = provide_scratch(c, m[g].weights, v[g].rows, d->workspace, d->workspace_bytes, off[g], cs, scratch);
-        p->calls.push_back(make_call(c, m[g], v[g]));
-        p->scratch.push_back(scratch);
+    {
+        const st::DeviceWeights& w0 = m[0].weights->device;
+        p->grouped = st::plan_grouped(w0.inputs, w0.outputs, w0.bits, (int)m.size(), c->sm_count);
+        p->inputs = w0.inputs; p->outputs = w0.outputs; p->codebook = w0.codebook;
+        p->problem_count = (int)m.size();
+        unsigned char* base = static_cast<unsigned char*>(d->workspace);
+        p->problems = reinterpret_cast<st::GroupedProblem*>(base);
+        const size_t table = st::align_up(m.size() * sizeof(st::GroupedProblem));
+        const size_t each = p->grouped.counter_bytes_per_problem + p->grouped.partial_bytes_per_problem;
+        std::vector<st::GroupedProblem> host(m.size());
+        for (size_t g = 0; g < m.size(); ++g) {
+            st::GroupedProblem& pr = host[g];
+            pr = st::GroupedProblem{};
+            pr.w = m[g].weights->device;
+            pr.x = static_cast<const float*>(m[g].input.data);
+            pr.y = static_cast<float*>(m[g].output.data);
+            pr.x_stride = (long long)v[g].x_stride;
+            pr.y_stride = (long long)v[g].y_stride;
+            pr.rows = v[g].rows;
+            for (int k = 0; k < pr.rows; ++k) pr.x_row[k] = pr.y_row[k] = k;
+            pr.counters = reinterpret_cast<unsigned int*>(base + table + g * each);
+            pr.partials = reinterpret_cast<float*>(base + table + g * each + p->grouped.counter_bytes_per_problem);
+        }
+        cudaError_t e = cudaMemsetAsync(base + table, 0, m.size() * each, cs);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(p->problems, host.data(), host.size() * sizeof(st::GroupedProblem),
+                                cudaMemcpyHostToDevice, cs);
+        const cudaError_t done = cudaStreamSynchronize(cs);  // `host` leaves scope; counters are zero for every replay
+        s = cuda_status(e != cudaSuccess ? e : done);
     }
-    if (s == STRIX_SUCCESS) s = cuda_status(cudaStreamSynchronize(cs));
     if (s != STRIX_SUCCESS) { delete p; return s; }
     for (auto& one : m) { p->retained.push_back(one.weights); ++one.weights->plan_refs; }
     *out = reinterpret_cast<strix_grouped_gemv_plan>(p);
