@@ -120,6 +120,7 @@ class ExpertParallelMoE:
         self.out_rows = torch.zeros((rows, model), **f32)
         self.back = self.out_rows if world == 1 else torch.zeros((rows, model), **f32)
         self.ones = torch.ones((rows,), **f32)
+        self.rank_ids = torch.arange(world, device="cuda")
         self.plan = MoePlan(ctx, local_experts, self.recv_x, self.out_rows, self.recv_ids, self.ones, device_routed=True)
         self.graphs = []
 
@@ -136,23 +137,21 @@ class ExpertParallelMoE:
         count = tokens * top_k
         flat = ids.reshape(-1)
         owner = flat // self.per_rank
-        order = torch.argsort(owner, stable=True)  # routes grouped by owner rank, slot order kept
-        sorted_owner = owner[order]
-        per_owner = torch.zeros(self.world, dtype=torch.long, device="cuda").scatter_add_(
-            0, owner, torch.ones_like(owner))
-        first = torch.cumsum(per_owner, 0) - per_owner
-        slot = sorted_owner * self.cap + (torch.arange(count, device="cuda") - first[sorted_owner])
+        # slot of a route in the send buffer: its owner's section, then its rank among the routes
+        # of this rank that go to the same owner, in route order (a running count per owner)
+        mine = owner[:, None] == self.rank_ids[None, :]
+        position = torch.cumsum(mine, 0).gather(1, owner[:, None]).squeeze(1) - 1
+        slot = owner * self.cap + position
         self.send_ids.fill_(self.INVALID)
-        self.send_ids[slot] = (flat[order] % self.per_rank).int()
-        self.send_x[slot] = x[order // top_k]
+        self.send_ids[slot] = (flat - owner * self.per_rank).int()
+        self.send_x[slot] = x.repeat_interleave(top_k, dim=0)
         if self.world > 1:
             dist.all_to_all_single(self.recv_x, self.send_x, group=self.group)
             dist.all_to_all_single(self.recv_ids, self.send_ids, group=self.group)
         self.plan.submit()
         if self.world > 1:
             dist.all_to_all_single(self.back, self.out_rows, group=self.group)
-        each = torch.empty((count, self.model), dtype=torch.float32, device="cuda")
-        each[order] = self.back[slot]
+        each = self.back[slot] if count else self.back[:0]
         y = torch.empty((tokens, self.model), dtype=torch.float32, device="cuda")
         if tokens:  # ascending slot order from +0, a zero score skips its slot: the plan's own combine
             self.ctx.moe_combine(each.view(tokens, top_k, self.model), scores.contiguous(), y, alpha=alpha)
