@@ -17,6 +17,13 @@ output rows copied back to pinned host memory after them, inside the timed regio
 With N>1 (launched under torchrun) every rank runs the same workload on its own GPU
 (replicas: the plain GEMV has no cross-GPU exchange) and the value is the sum.
 
+`extra` in the JSON line carries the other configurations of the metric, measured outside
+the timed region: rates x rows on the largest shape, the prefill GEMM (K4/K5/K6), the
+routed-expert block on one rank's bank, and at every N the tensor-parallel dense layers
+(row-parallel + all-reduce, LM head + all-gather) and the expert-parallel block
+(all-to-all dispatch and return).  `--no-extra` skips them; `--case gemv|gemm|moe` runs one
+small fixed workload of one kernel for profilers.
+
 `--impl reference` times the CPU contract (this repository's C restatement of the
 reference's NumPy path, all host threads) on a bounded sample of the same workload.
 """
