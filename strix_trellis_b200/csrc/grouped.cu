@@ -151,13 +151,15 @@ __global__ void __launch_bounds__(kThreadsG, 2) grouped_linear_kernel(const Grou
         const float v10 = acc[0][2] + acc[1][2], v11 = acc[0][3] + acc[1][3];
         if (r0 < rows) { p[r0 * 128 + col] = v00; p[r0 * 128 + col + 8] = v10; }
         if (r0 + 1 < rows) { p[(r0 + 1) * 128 + col] = v01; p[(r0 + 1) * 128 + col + 8] = v11; }
-        __threadfence();
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned int seen = atomicAdd(&pr.counters[nb], 1u);
+        // one release/acquire atomic: the CTA's planes (ordered before it by the barrier) are
+        // visible before the count, and the last arriver sees the planes of the others
+        unsigned int seen;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(seen) : "l"(pr.counters + nb) : "memory");
         const int last = (seen == (unsigned int)args.splits - 1);
-        if (last) { pr.counters[nb] = 0; __threadfence(); }
+        if (last) pr.counters[nb] = 0;  // visible at grid end, before any later launch
         s_last = last && !s_abort;
     }
     __syncthreads();
