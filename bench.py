@@ -614,7 +614,7 @@ def run_gpu(args):
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_kind": peak_kind,
                          "traffic": None if traffic is None else round(traffic * total_bytes / launches),
-                         "kernel": "gemv_fused_kernel<4, mul1>",
+                         "kernel": "gemv_fused_kernel<4, mul1, one row>",
                          "algorithmic_bytes_per_launch": round(total_bytes / launches)},
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
