@@ -11,7 +11,7 @@ What is stored is what the reference computed: SHA-256 of every bit-exact stage
 (decoded Q, scaled fp16, input H128, core input, sequential fp32 core, output) and
 the float32 outputs themselves for tolerance comparisons.
 
-Files written:
+Files written (STGPU001 containers come from make_stgpu.py):
   grid.json / grid_ref.npz   the reference's 48-case correctness grid (bits 1..8 x
                              3 codebooks x two orientations, 8 rows)
   config1.json / config1.npz 4096x4096 K4 mul1, one fp16 N(0,1) row (benchmark config 1)
