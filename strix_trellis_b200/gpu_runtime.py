@@ -1,13 +1,15 @@
 """Fixture-driven check of the runtime on the GPU, with the coverage of the reference's
 `gpu_runtime` executable (reference `docs/GPU_TESTS.md:70-124`):
 
-    python -m strix_trellis_b200.gpu_runtime [--route all|gemv|gemm|grouped|stages] fixture.stgpu [...]
+    python -m strix_trellis_b200.gpu_runtime [--route all|gemv|gemm|grouped|stages|moe] fixture.stgpu | directory [...]
 
 Every number the checks compare against comes from the fixture file (written by the
 reference's CPU contract); alpha and beta are applied to it here in binary32 with a separate
 multiplication and addition.  Any API, format, stage or tolerance failure gives a nonzero
 exit status.  STRANK01 projection files are accepted too (route gemv / gemm only: they carry
-no stage checkpoints) and are held to their own per-output bound as well.
+no stage checkpoints) and are held to their own per-output bound as well.  A DIRECTORY holding
+the six `expert-{gate,up,down}-k{2,3}.strank` files and `moe-*.strank` windows of the reference's
+rank generator is run as routed-expert blocks (route moe).
 """
 from __future__ import annotations
 
@@ -19,8 +21,10 @@ import numpy as np
 import torch
 
 from . import native as N
-from .fixtures import GpuFixture, RankFixture, read_fixture
-from .runtime import Context, _cur_stream
+from pathlib import Path
+
+from .fixtures import GpuFixture, RankFixture, RouteWindowFixture, read_fixture, read_strank
+from .runtime import Context, MoePlan, _cur_stream
 
 ALPHA_BETA = ((1.0, 0.0), (-0.75, 0.25), (0.0, -0.5), (1.0, -0.0))
 GEMV_ROWS = tuple(range(0, 9))
@@ -192,6 +196,76 @@ def route_grouped(rep, ctx, fx: GpuFixture, w):
     muted.close()
 
 
+# ---- routed-expert windows ------------------------------------------------------------
+# How the reference's generator derives a bank of experts from its six projection files
+# (tools/make_rank_fixtures.py:127-145): bank id = 17 + 3*index; the rate of each projection
+# and a per-expert bias offset depend on the index.
+MOE_NRMSE = 1e-4  # three chained projections with a binary16 rounding between them
+
+
+def _expert_index(expert_id):
+    return (int(expert_id) - 17) // 3
+
+
+def _expert_bits(index, projection):
+    if projection == "gate":
+        return 2 + index % 2
+    if projection == "up":
+        return 3 if index % 3 == 0 else 2
+    return 2 if index % 3 == 1 else 3
+
+
+def _expert_bias(base, index, projection):
+    factor = {"gate": 1.0, "up": -0.5, "down": 0.25}[projection]
+    return (base.astype(np.float32) + np.float32((17 + 3 * index + 1) * factor / 512)).astype(np.float32)
+
+
+def route_moe(rep, ctx, directory):
+    directory = Path(directory)
+    files = {(p, k): read_strank(directory / f"expert-{p}-k{k}.strank")
+             for p in ("gate", "up", "down") for k in (2, 3)}
+    x = files[("gate", 2)].x  # gate and up projections share one input
+    windows = sorted(directory.glob("moe-*.strank"))
+    rep.line(bool(windows), f"{directory.name}: {len(windows)} routed-expert windows")
+    for path in windows:
+        fx = read_strank(path)
+        if not isinstance(fx, RouteWindowFixture):
+            rep.line(False, f"{path.name}: not a routed-expert window")
+            continue
+        ids = np.unique(fx.routes)
+        experts = []
+        for eid in ids:
+            index, triple = _expert_index(eid), []
+            for projection in ("gate", "up", "down"):
+                f = files[(projection, _expert_bits(index, projection))]
+
+                class Layer:
+                    trellis, suh, svh, bits, codebook = f.trellis, f.suh, f.svh, f.bits, f.codebook
+                    bias = _expert_bias(f.bias, index, projection)
+                triple.append(ctx.prepare(Layer))
+            experts.append(tuple(triple))
+        rows = fx.meta.rows
+        for alpha, beta in ALPHA_BETA:
+            y = _dev(fx.old) if beta != 0.0 else _fresh(fx.ref.shape, nan=True)
+            plan = MoePlan(ctx, experts, _dev(x[:rows]), y, fx.routes, fx.scores, expert_ids=ids, alpha=alpha, beta=beta)
+            plan.submit()
+            torch.cuda.synchronize()
+            got, hidden = y.cpu().numpy(), plan.hidden().cpu().numpy()
+            plan.close()
+            want = expected(fx.ref, fx.old, alpha, beta)
+            diff = np.abs(got.astype(np.float64) - want)
+            finite = bool(np.isfinite(got).all())
+            nrmse = float(np.sqrt((diff ** 2).sum() / max(float((want.astype(np.float64) ** 2).sum()), 1e-30)))
+            ok = finite and diff.max() <= MAXABS * max(1.0, float(np.abs(want).max())) and nrmse <= MOE_NRMSE
+            rep.line(ok, f"{fx.name} block experts={len(ids)} alpha={alpha} beta={beta} maxabs={diff.max():.3e} "
+                         f"maxref={np.abs(want).max():.3e} nrmse={nrmse:.3e}")
+        live = fx.scores != 0  # a zero score skips its slot: nothing is written there
+        rep.tolerance(f"{fx.name} SwiGLU values of the scored slots", hidden[live], fx.hidden[live])
+        for triple in experts:
+            for w in triple:
+                w.close()
+
+
 ROUTES = {"stages": route_stages, "gemv": route_gemv, "gemm": route_gemm, "grouped": route_grouped}
 
 
@@ -205,6 +279,13 @@ def run(paths, route="all", out=sys.stdout):
     stream = torch.cuda.Stream()  # explicit non-blocking stream for uploads, launches and downloads
     with torch.cuda.stream(stream):
         for path in paths:
+            if Path(path).is_dir():
+                if route in ("all", "moe"):
+                    route_moe(rep, ctx, path)
+                continue
+            if route == "moe":
+                rep.line(False, f"{path}: route moe takes a directory")
+                continue
             fx = read_fixture(path)
             if not isinstance(fx, (GpuFixture, RankFixture)):
                 rep.line(False, f"{path}: routed-expert windows are not a matmul fixture")
@@ -225,7 +306,7 @@ def run(paths, route="all", out=sys.stdout):
 
 def main(argv=None):
     p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    p.add_argument("--route", choices=["all", *ROUTES], default="all")
+    p.add_argument("--route", choices=["all", *ROUTES, "moe"], default="all")
     p.add_argument("fixtures", nargs="+")
     a = p.parse_args(argv)
     return 1 if run(a.fixtures, a.route) else 0

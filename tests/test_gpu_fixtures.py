@@ -50,3 +50,63 @@ def test_harness_notices_a_wrong_reference(tmp_path):
     assert any("Q[" in l for l in failing(log))
     assert gpu_runtime.main(["--route", "gemv", str(bad)]) == 1
     assert gpu_runtime.main(["--route", "gemv", str(FILES[0])]) == 0
+
+
+def test_moe_route_over_a_generated_directory(tmp_path):
+    """A directory in the layout of the reference's rank generator (six projection files, one
+    routed window), at a small size and with the CPU contract as the source of `ref`."""
+    import struct
+    from oracle import c_oracle
+    from strix_trellis_b200 import gpu_runtime, synthetic
+    from test_fixture_reader import container
+    model, inter, rows, top_k, bank = 256, 128, 8, 6, 12
+    x = synthetic.make_activations(rows, model, seed=9701)
+    layers = {}
+    for pi, (p, i, n) in enumerate((("gate", model, inter), ("up", model, inter), ("down", inter, model))):
+        for k in (2, 3):
+            l = synthetic.make_layer(i, n, k, 9710 + 10 * pi + k, bias=True)
+            layers[(p, k)] = l
+            xin = x if p != "down" else synthetic.make_activations(rows, inter, seed=9702)
+            ref = c_oracle.linear(l.trellis, l.suh, l.svh, l.bias, k, 2, xin)
+            base = c_oracle.linear(l.trellis, l.suh, l.svh, None, k, 2, xin)
+            meta = struct.pack("<8I", i, n, k, 2, 0x83DCD12D, rows, 1, 9710 + pi)
+            sections = [("meta", meta), ("trellis", l.trellis.astype("<u2").tobytes()),
+                        ("suh", l.suh.astype("<f2").tobytes()), ("svh", l.svh.astype("<f2").tobytes()),
+                        ("bias", l.bias.astype("<f4").tobytes()), ("x", xin.astype("<f4").tobytes()),
+                        ("old", np.zeros((rows, n), "<f4").tobytes()), ("ref", ref.tobytes()),
+                        ("base", base.tobytes()), ("bound", np.full((rows, n), 1e-3, "<f8").tobytes())]
+            (tmp_path / f"expert-{p}-k{k}.strank").write_bytes(container(b"STRANK01", sections))
+    index = np.array([[(3 * r + s) % bank for s in range(top_k)] for r in range(rows)])
+    scores = np.array([[1 + (r % 3) + s for s in range(top_k)] for r in range(rows)], "<f4")
+    scores[1::3, 5] = 0
+    scores /= scores.sum(axis=1, keepdims=True)
+    hidden = np.zeros((rows, top_k, inter), "<f4")
+    each = np.zeros((rows, top_k, model), "<f4")
+    out = np.zeros((rows, model), np.float32)
+    for s in range(top_k):
+        for r in range(rows):
+            e = int(index[r, s])
+            proj = {}
+            for p in ("gate", "up", "down"):
+                l = layers[(p, gpu_runtime._expert_bits(e, p))]
+                proj[p] = (l, gpu_runtime._expert_bias(l.bias, e, p))
+            g, u = (c_oracle.linear(proj[p][0].trellis, proj[p][0].suh, proj[p][0].svh, proj[p][1],
+                                    proj[p][0].bits, 2, x[r:r + 1]) for p in ("gate", "up"))
+            hidden[r, s] = c_oracle.swiglu(g, u)[0]
+            d = proj["down"]
+            each[r, s] = c_oracle.linear(d[0].trellis, d[0].suh, d[0].svh, d[1], d[0].bits, 2, hidden[r, s][None])[0]
+            if scores[r, s] != 0:
+                out[r] += each[r, s] * scores[r, s]
+    old = synthetic.make_activations(rows, model, seed=9703)
+    meta = struct.pack("<8I", model, model, 0, 2, 0x83DCD12D, rows, 0, 9700)
+    window = [("meta", meta), ("routes", (17 + 3 * index).astype("<u4").tobytes()), ("scores", scores.tobytes()),
+              ("hidden", hidden.tobytes()), ("each", each.tobytes()), ("ref", out.astype("<f4").tobytes()),
+              ("old", old.astype("<f4").tobytes())]
+    (tmp_path / "moe-overlap.strank").write_bytes(container(b"STRANK01", window))
+    log = io.StringIO()
+    failures = gpu_runtime.run([tmp_path], "moe", out=log)
+    assert failures == 0, "\n".join(failing(log))
+    assert sum(l.startswith("PASS") and " block " in l for l in log.getvalue().splitlines()) == 4
+    # the six projection files as plain matmul fixtures, held to their own bound too
+    log = io.StringIO()
+    assert gpu_runtime.run(sorted(tmp_path.glob("expert-*.strank")), "gemv", out=log) == 0, "\n".join(failing(log))
