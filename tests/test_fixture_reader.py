@@ -148,3 +148,30 @@ def test_rank_containers(tmp_path):
     assert isinstance(got, F.RouteWindowFixture)
     assert got.routes.shape == (rows, top_k) and got.hidden.shape == (rows, top_k, inter)
     assert bits_equal(got.each, each) and bits_equal(got.scores, scores)
+
+
+def test_harness_expectation_and_criterion():
+    """Host side of the fixture harness: alpha/beta applied with separate roundings, a zero
+    beta of either sign never reads the old output, and the two-part criterion."""
+    import io
+    from strix_trellis_b200 import gpu_runtime as G
+    ref = np.array([[1.0, -2.5, 3.0e-3]], np.float32)
+    old = np.array([[np.nan, np.inf, 7.0]], np.float32)
+    for beta in (0.0, -0.0):
+        assert bits_equal(G.expected(ref, old, -0.75, beta), (np.float32(-0.75) * ref).astype(np.float32))
+    old = np.array([[0.1, 0.2, 0.3]], np.float32)
+    want = trellis_ref.apply_alpha_beta(ref, -0.75, 0.25, old)
+    assert bits_equal(G.expected(ref, old, -0.75, 0.25), want)
+    rep = G.Report(io.StringIO())
+    rep.tolerance("exact", ref, ref)
+    rep.tolerance("inside", ref + np.float32(2e-6), ref)
+    assert rep.failures == 0
+    rep.tolerance("maxabs", ref + np.array([[0, 0, 2e-3]], np.float32), ref)      # 2e-3 > 5e-4*max(1, 2.5)
+    rep.tolerance("nrmse", ref + np.float32(2e-4), ref)                            # inside maxabs, NRMSE 8.9e-5
+    rep.tolerance("nan", np.array([[1.0, np.nan, 0.0]], np.float32), ref)
+    rep.tolerance("bound", ref + np.float32(2e-6), ref, bound=np.full(ref.shape, 1e-6))
+    rep.identical("bytes", np.float32([0.0]), np.float32([-0.0]))                  # signed zeros count
+    assert rep.failures == 5 and rep.checks == 7
+    assert [G._expert_bits(i, p) for i in range(3) for p in ("gate", "up", "down")] == [2, 3, 3, 3, 2, 2, 2, 2, 3]
+    assert G._expert_index(17 + 3 * 11) == 11
+    assert G._expert_bias(np.zeros(2, np.float32), 1, "up")[0] == np.float32(-21 * 0.5 / 512)
