@@ -326,7 +326,8 @@ def ep_case(torch, dist, ctx, stream, rank, world, tokens_list=(1, 8, 64), exper
             def forward():
                 turn[0] = (turn[0] + 1) % 4
                 return run(xh, *on_device[turn[0]])
-            us = time_calls(torch, stream, forward, reps, warm=2)
+            # more than one rank: the first all-to-alls also set up NCCL's peer connections
+            us = time_calls(torch, stream, forward, reps if world == 1 else 2 * reps, warm=2 if world == 1 else 6)
             tt = torch.tensor([us], device="cuda")
             if world > 1:
                 dist.all_reduce(tt, op=dist.ReduceOp.MAX)
