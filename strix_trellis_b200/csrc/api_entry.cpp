@@ -249,6 +249,8 @@ strix_status strix_context_create(const strix_context_desc* d, strix_context* ou
     e = cudaGetDevice(&active);
     if (e != cudaSuccess) return cuda_status(e);
     if (active != d->device_ordinal) return STRIX_ERROR_INVALID_ARGUMENT;  // never switches devices
+    e = st::configure_device();  // function attributes of this device; the active device is the context's
+    if (e != cudaSuccess) return cuda_status(e);
     strix_context_impl* c = new (std::nothrow) strix_context_impl;
     if (!c) return STRIX_ERROR_OUT_OF_MEMORY;
     c->device = d->device_ordinal;

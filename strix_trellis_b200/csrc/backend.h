@@ -35,6 +35,11 @@ struct LinearCall {
     unsigned int* status;  // device word that collects bounded-wait failures (may be null)
 };
 
+// Per-device set-up of every kernel in the library (the opt-in to more than 48 KB of dynamic
+// shared memory is a function attribute of ONE device).  Runs when a context is created, with
+// the context's device current; launches never set attributes.
+cudaError_t configure_device();
+
 constexpr size_t kAlign = 256;
 inline size_t align_up(size_t v, size_t a = kAlign) { return (v + a - 1) / a * a; }
 

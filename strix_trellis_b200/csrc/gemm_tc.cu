@@ -427,15 +427,30 @@ GemmPlan plan_gemm(const DeviceWeights& w, int rows, int sm_count) {
 
 template <int K, int CB>
 static cudaError_t launch_tc(const GemmArgs& args, int grid, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<K, CB>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
     gemm_tc_kernel<K, CB><<<grid, kThreadsTc, kSmemTc, stream>>>(args);
     return cudaGetLastError();
+}
+
+// Opt-in dynamic shared memory is a per-device function attribute: set for every instantiation
+// when a context is created on a device (configure_device), never on the launch path.
+template <int CB>
+static cudaError_t configure_gemm_tc_kernels_codebook() {
+    cudaError_t e = cudaSuccess;
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<1, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<2, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<3, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<4, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<5, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<6, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<7, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<8, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+    return e;
+}
+cudaError_t configure_gemm_tc_kernels() {
+    cudaError_t e = configure_gemm_tc_kernels_codebook<CB_3INST>();
+    if (e == cudaSuccess) e = configure_gemm_tc_kernels_codebook<CB_MCG>();
+    if (e == cudaSuccess) e = configure_gemm_tc_kernels_codebook<CB_MUL1>();
+    return e;
 }
 
 template <int CB>

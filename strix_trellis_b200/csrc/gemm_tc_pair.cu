@@ -315,13 +315,6 @@ int gemm_pair_rows_padded(int rows) { return (rows + 511) / 512 * 512; }
 
 template <int K, int CB>
 static cudaError_t launch_pair(const PairArgs& args, int grid, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<K, CB>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreadsP);
@@ -335,6 +328,28 @@ static cudaError_t launch_pair(const PairArgs& args, int grid, cudaStream_t stre
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<K, CB>, args);
+}
+
+// Opt-in dynamic shared memory is a per-device function attribute: set for every instantiation
+// when a context is created on a device (configure_device), never on the launch path.
+template <int CB>
+static cudaError_t configure_gemm_pair_kernels_codebook() {
+    cudaError_t e = cudaSuccess;
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<1, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<2, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<3, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<4, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<5, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<6, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<7, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<8, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+    return e;
+}
+cudaError_t configure_gemm_pair_kernels() {
+    cudaError_t e = configure_gemm_pair_kernels_codebook<CB_3INST>();
+    if (e == cudaSuccess) e = configure_gemm_pair_kernels_codebook<CB_MCG>();
+    if (e == cudaSuccess) e = configure_gemm_pair_kernels_codebook<CB_MUL1>();
+    return e;
 }
 
 template <int CB>

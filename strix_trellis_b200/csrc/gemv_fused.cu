@@ -44,6 +44,7 @@ constexpr int kThreads = (kConsumers + 2) * 32;  // + producer warp + epilogue w
 constexpr int kDumpThreads = (kConsumers + 1) * 32;  // decode warps + epilogue warp
 constexpr uint32_t kEmptyWord = 0xFFFFFFFFu;      // a partial-plane word nobody has written yet
 constexpr int kActBytes = 64 * 1024;             // staged core input per CTA
+constexpr size_t kGemvSmemLimit = 200 * 1024;    // dynamic shared memory a launch may ask for
 #ifndef ST_GEMV_OCCUPANCY
 #define ST_GEMV_OCCUPANCY 1
 #endif
@@ -469,13 +470,6 @@ GemvPlan plan_gemv(const DeviceWeights& w, int rows, int sm_count) {
 
 template <int K, int CB, bool MULTI>
 static cudaError_t launch_rows(const GemvArgs& args, int grid, size_t smem, bool pdl, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(gemv_fused_kernel<K, CB, MULTI>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
@@ -509,6 +503,36 @@ static cudaError_t launch_bits(const GemvArgs& a, int g, size_t smem, bool pdl, 
     case 8: return launch_one<8, CB>(a, g, smem, pdl, s);
     default: return cudaErrorInvalidValue;
     }
+}
+
+// Opt-in dynamic shared memory is a per-device function attribute: set for every instantiation
+// when a context is created on a device (configure_device), never on the launch path.
+template <int K, int CB>
+static cudaError_t configure_rate() {
+    cudaError_t e = cudaFuncSetAttribute(gemv_fused_kernel<K, CB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kGemvSmemLimit);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemv_fused_kernel<K, CB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kGemvSmemLimit);
+    return e;
+}
+template <int CB>
+static cudaError_t configure_codebook() {
+    cudaError_t e = configure_rate<1, CB>();
+    if (e == cudaSuccess) e = configure_rate<2, CB>();
+    if (e == cudaSuccess) e = configure_rate<3, CB>();
+    if (e == cudaSuccess) e = configure_rate<4, CB>();
+    if (e == cudaSuccess) e = configure_rate<5, CB>();
+    if (e == cudaSuccess) e = configure_rate<6, CB>();
+    if (e == cudaSuccess) e = configure_rate<7, CB>();
+    if (e == cudaSuccess) e = configure_rate<8, CB>();
+    return e;
+}
+cudaError_t configure_gemv_kernels() {
+    cudaError_t e = configure_codebook<CB_3INST>();
+    if (e == cudaSuccess) e = configure_codebook<CB_MCG>();
+    if (e == cudaSuccess) e = configure_codebook<CB_MUL1>();
+    return e;
 }
 
 cudaError_t reset_gemv_scratch(void* workspace, const GemvPlan& plan, cudaStream_t stream) {

@@ -17,6 +17,7 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kThreadsG = (kWarps + 1) * 32;
 constexpr int kMaxStages = 16;
+constexpr size_t kGroupedSmemLimit = 110 * 1024;  // dynamic shared memory a launch may ask for (two CTAs per SM)
 
 struct GroupedArgs {
     const GroupedProblem* problems;
@@ -212,15 +213,19 @@ GroupedPlan plan_grouped(int inputs, int outputs, int max_bits, int problems, in
     return plan;
 }
 
+// Opt-in dynamic shared memory is a per-device function attribute: set when a context is created
+// on a device (configure_device), never on the launch path.
+cudaError_t configure_grouped_kernels() {
+    cudaError_t e = cudaFuncSetAttribute(grouped_linear_kernel<CB_3INST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGroupedSmemLimit);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(grouped_linear_kernel<CB_MCG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGroupedSmemLimit);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(grouped_linear_kernel<CB_MUL1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGroupedSmemLimit);
+    return e;
+}
+
 template <int CB>
 static cudaError_t launch_grouped_cb(const GroupedArgs& args, int grid, size_t smem, bool pdl, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(grouped_linear_kernel<CB>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(110 * 1024));
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreadsG);
@@ -241,7 +246,7 @@ cudaError_t launch_grouped(const GroupedProblem* problems, int problem_count, in
     (void)outputs;
     GroupedArgs args{problems, plan.ctas_per_problem, plan.splits, plan.stages, inputs / 128, plan.stage_stride, status};
     const long long grid = (long long)problem_count * plan.ctas_per_problem;
-    if (grid > 0x7FFFFFFF || plan.smem_bytes > 110 * 1024) return cudaErrorInvalidValue;
+    if (grid > 0x7FFFFFFF || plan.smem_bytes > kGroupedSmemLimit) return cudaErrorInvalidValue;
     switch (codebook) {
     case CB_3INST: return launch_grouped_cb<CB_3INST>(args, (int)grid, plan.smem_bytes, programmatic, stream);
     case CB_MCG: return launch_grouped_cb<CB_MCG>(args, (int)grid, plan.smem_bytes, programmatic, stream);
