@@ -6,67 +6,67 @@
 
 namespace sapi {
 
+// Every device call is made with the context's device current; the library never switches.
 strix_status context_check(strix_context c) {
-    if (!c) return STRIX_ERROR_INVALID_ARGUMENT;
-    int device = -1;
-    const cudaError_t e = cudaGetDevice(&device);
+    if (c == nullptr) return STRIX_ERROR_INVALID_ARGUMENT;
+    int current = -1;
+    const cudaError_t e = cudaGetDevice(&current);
     if (e != cudaSuccess) return cuda_status(e);
-    return device == c->device ? STRIX_SUCCESS : STRIX_ERROR_INVALID_ARGUMENT;
+    return current == c->device ? STRIX_SUCCESS : STRIX_ERROR_INVALID_ARGUMENT;
 }
 
+// The stream travels in the descriptor's pointer field.  The null stream needs no look-up;
+// any other handle must be a live stream of the context's device.
 strix_status stream_check(strix_context c, const strix_stream* s, cudaStream_t& out) {
-    const strix_status st = header(s);
-    if (st != STRIX_SUCCESS) return st;
-    out = reinterpret_cast<cudaStream_t>(s->hip_stream);
-    if (!out) return STRIX_SUCCESS;
-    int device = -1;
+    const strix_status verdict = header(s);
+    if (verdict != STRIX_SUCCESS) return verdict;
+    out = static_cast<cudaStream_t>(s->hip_stream);
+    if (out == nullptr) return STRIX_SUCCESS;
+    int home = -1;
     unsigned int flags = 0;
-    if (cudaStreamGetDevice(out, &device) != cudaSuccess ||
-        cudaStreamGetFlags(out, &flags) != cudaSuccess || device != c->device) {
-        (void)cudaGetLastError();
-        return STRIX_ERROR_INVALID_ARGUMENT;
-    }
-    return STRIX_SUCCESS;
+    const bool alive = cudaStreamGetDevice(out, &home) == cudaSuccess && cudaStreamGetFlags(out, &flags) == cudaSuccess;
+    if (!alive) (void)cudaGetLastError();
+    return alive && home == c->device ? STRIX_SUCCESS : STRIX_ERROR_INVALID_ARGUMENT;
 }
 
-// cuMemGetAddressRange through the runtime's driver entry point table: the library
-// does not link libcuda, so it loads on machines without a driver.
-typedef int (*AddressRangeFn)(unsigned long long*, size_t*, unsigned long long);
-static AddressRangeFn address_range_fn() {
-    static AddressRangeFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess) {
-            (void)cudaGetLastError();
-            return (AddressRangeFn) nullptr;
-        }
-        return reinterpret_cast<AddressRangeFn>(p);
+// The allocation that holds an address, from the driver (cuMemGetAddressRange), reached
+// through the runtime's entry-point table so that the library has no link-time dependency on
+// the driver library.
+namespace {
+struct Allocation { uintptr_t base; size_t bytes; };
+bool containing_allocation(const void* p, Allocation& found) {
+    using Query = int (*)(unsigned long long*, size_t*, unsigned long long);
+    static const Query query = [] {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult how;
+        const bool ok = cudaGetDriverEntryPoint("cuMemGetAddressRange", &entry, cudaEnableDefault, &how) == cudaSuccess &&
+                        how == cudaDriverEntryPointSuccess;
+        if (!ok) (void)cudaGetLastError();
+        return ok ? reinterpret_cast<Query>(entry) : static_cast<Query>(nullptr);
     }();
-    return fn;
+    unsigned long long base = 0;
+    size_t bytes = 0;
+    if (!query || query(&base, &bytes, static_cast<unsigned long long>(reinterpret_cast<uintptr_t>(p))) != 0) return false;
+    found = Allocation{static_cast<uintptr_t>(base), bytes};
+    return true;
 }
+}  // namespace
 
 strix_status device_buffer(strix_context c, const void* p, uint64_t bytes, uint64_t align) {
-    if (!bytes) return STRIX_SUCCESS;
-    if (!p || !range_ok(p, bytes) || reinterpret_cast<uintptr_t>(p) % align)
-        return STRIX_ERROR_INVALID_ARGUMENT;
-    cudaPointerAttributes attr{};
-    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    if (bytes == 0) return STRIX_SUCCESS;  // an empty buffer is never looked at
+    const uintptr_t at = reinterpret_cast<uintptr_t>(p);
+    if (p == nullptr || at % align != 0 || !range_ok(p, bytes)) return STRIX_ERROR_INVALID_ARGUMENT;
+    cudaPointerAttributes kind{};
+    if (cudaPointerGetAttributes(&kind, p) != cudaSuccess) {
         (void)cudaGetLastError();
         return STRIX_ERROR_INVALID_ARGUMENT;
     }
-    if (attr.type != cudaMemoryTypeDevice || attr.device != c->device)
-        return STRIX_ERROR_INVALID_ARGUMENT;  // host, registered host and managed memory
-    AddressRangeFn range = address_range_fn();
-    if (!range) return STRIX_ERROR_INVALID_ARGUMENT;
-    unsigned long long base = 0;
-    size_t size = 0;
-    if (range(&base, &size, (unsigned long long)reinterpret_cast<uintptr_t>(p)) != 0)
-        return STRIX_ERROR_INVALID_ARGUMENT;
-    const uintptr_t at = reinterpret_cast<uintptr_t>(p);
-    if (at < base || at - base > size || bytes > size - (at - base))
-        return STRIX_ERROR_INSUFFICIENT_BUFFER;
-    return STRIX_SUCCESS;
+    // plain device memory of this device only: no host, pinned-host or managed memory
+    if (kind.type != cudaMemoryTypeDevice || kind.device != c->device) return STRIX_ERROR_INVALID_ARGUMENT;
+    Allocation owner{};
+    if (!containing_allocation(p, owner)) return STRIX_ERROR_INVALID_ARGUMENT;
+    const bool inside = at >= owner.base && at - owner.base <= owner.bytes && bytes <= owner.bytes - (at - owner.base);
+    return inside ? STRIX_SUCCESS : STRIX_ERROR_INSUFFICIENT_BUFFER;
 }
 
 // ---- tensors ----------------------------------------------------------------------

@@ -14,154 +14,172 @@ struct strix_linear_plan_impl {
 
 namespace {
 
-struct Region { uint64_t offset, bytes; };
+// ---- what a layer consists of ------------------------------------------------------------
+// Four regions in transport order.  Their sizes follow from the geometry; each starts on a
+// multiple of its element size inside a blob; only the bias may be absent.
+enum : int { kTiles = 0, kInputScales, kOutputScales, kBias, kRegionCount };
+struct RegionRule {
+    uint64_t element_bytes;
+    bool optional;
+};
+constexpr RegionRule kRegionRules[kRegionCount] = {{4, false}, {2, false}, {2, false}, {4, true}};
 
-strix_status metadata_check(const strix_exl3_metadata_v1& m, uint64_t rows, uint64_t columns) {
-    if (m.struct_size != sizeof(m) || m.transport_version != STRIX_TRELLIS_TRANSPORT_VERSION)
-        return STRIX_ERROR_ABI_MISMATCH;
-    for (uint64_t v : m.reserved)
-        if (v) return STRIX_ERROR_INVALID_ARGUMENT;
-    if (m.flags) return STRIX_ERROR_INVALID_ARGUMENT;
-    if (m.rows != rows || m.columns != columns || !m.rows || !m.columns || m.rows > INT_MAX ||
-        m.columns > INT_MAX || m.rows % 128 || m.columns % 128)
-        return STRIX_ERROR_UNSUPPORTED_FORMAT;
-    if (m.bits_x2 < 2 || m.bits_x2 > 16 || m.bits_x2 % 2) return STRIX_ERROR_UNSUPPORTED_FORMAT;
-    uint32_t marker;
-    switch (enum_bits(m.codebook)) {
-    case STRIX_CODEBOOK_3INST: marker = STRIX_EXL3_MARKER_3INST; break;
-    case STRIX_CODEBOOK_MCG: marker = STRIX_EXL3_MARKER_MCG; break;
-    case STRIX_CODEBOOK_MUL1: marker = STRIX_EXL3_MARKER_MUL1; break;
-    default: return STRIX_ERROR_UNSUPPORTED_FORMAT;
+struct LayerGeometry {
+    uint64_t outputs = 0, inputs = 0;
+    uint32_t bits = 0, codebook = 0;
+    bool has_bias = false;
+};
+
+uint32_t marker_of(uint32_t codebook, bool& known) {
+    known = true;
+    switch (codebook) {
+    case STRIX_CODEBOOK_3INST: return STRIX_EXL3_MARKER_3INST;
+    case STRIX_CODEBOOK_MCG: return STRIX_EXL3_MARKER_MCG;
+    case STRIX_CODEBOOK_MUL1: return STRIX_EXL3_MARKER_MUL1;
+    default: known = false; return 0;
     }
-    if (marker != m.marker) return STRIX_ERROR_UNSUPPORTED_FORMAT;
-    const uint16_t probe = 1;
-    if (*reinterpret_cast<const unsigned char*>(&probe) != 1) return STRIX_ERROR_UNSUPPORTED_FORMAT;
-    uint64_t packed = 0;
-    if (!mul_ok(m.rows, m.columns, packed) || !mul_ok(packed / 8, m.bits_x2 / 2, packed))
+}
+
+// Geometry, rate, codebook and the byte count of every region; anything off is an
+// unsupported format.  `given[i]` are the byte counts the caller declared.
+strix_status geometry_check(uint64_t outputs, uint64_t inputs, uint32_t bits_x2, uint32_t codebook,
+                            uint32_t marker, const uint64_t (&given)[kRegionCount], LayerGeometry& g) {
+    const auto dimension_ok = [](uint64_t n) { return n >= 128 && n <= INT_MAX && n % 128 == 0; };
+    if (!dimension_ok(outputs) || !dimension_ok(inputs)) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    if (bits_x2 % 2 != 0 || bits_x2 < 2 || bits_x2 > 16) return STRIX_ERROR_UNSUPPORTED_FORMAT;  // integer rates 1..8
+    bool known = false;
+    if (marker_of(codebook, known) != marker || !known) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+#if defined(__BYTE_ORDER__) && __BYTE_ORDER__ != __ORDER_LITTLE_ENDIAN__
+    return STRIX_ERROR_UNSUPPORTED_FORMAT;  // transport words are little-endian and uploaded as they are
+#endif
+    uint64_t weights = 0, tile_bytes = 0;
+    if (!mul_ok(outputs, inputs, weights) || !mul_ok(weights / 8, bits_x2 / 2, tile_bytes))
         return STRIX_ERROR_UNSUPPORTED_FORMAT;
-    if (m.trellis_bytes != packed || m.suh_bytes != m.columns * 2 || m.svh_bytes != m.rows * 2 ||
-        (m.bias_bytes && m.bias_bytes != m.rows * 4) || (!m.bias_bytes && m.bias_offset))
-        return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    const uint64_t expected[kRegionCount] = {tile_bytes, inputs * 2, outputs * 2, outputs * 4};
+    for (int i = 0; i < kRegionCount; ++i) {
+        const bool absent = kRegionRules[i].optional && given[i] == 0;
+        if (!absent && given[i] != expected[i]) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    }
+    g.outputs = outputs;
+    g.inputs = inputs;
+    g.bits = bits_x2 / 2;
+    g.codebook = codebook;
+    g.has_bias = given[kBias] != 0;
     return STRIX_SUCCESS;
 }
 
-strix_status transport_check(const strix_exl3_transport_desc* d, strix_exl3_metadata_v1& m) {
+// Single-blob transport: descriptor, then the metadata record, then where the regions lie.
+strix_status blob_check(const strix_exl3_transport_desc* d, LayerGeometry& g, strix_host_region (&regions)[kRegionCount]) {
     strix_status s = header(d);
     if (s != STRIX_SUCCESS) return s;
-    if (enum_bits(d->format) != STRIX_TRANSPORT_EXL3_CANONICAL ||
-        d->transport_version != STRIX_TRELLIS_TRANSPORT_VERSION)
+    if (enum_bits(d->format) != STRIX_TRANSPORT_EXL3_CANONICAL || d->transport_version != STRIX_TRELLIS_TRANSPORT_VERSION)
         return STRIX_ERROR_UNSUPPORTED_FORMAT;
-    if (!d->metadata || d->metadata_bytes != sizeof(m)) return STRIX_ERROR_INVALID_ARGUMENT;
-    std::memcpy(&m, d->metadata, sizeof(m));
-    s = metadata_check(m, d->rows, d->columns);
+    strix_exl3_metadata_v1 m;
+    if (d->metadata == nullptr || d->metadata_bytes != sizeof m) return STRIX_ERROR_INVALID_ARGUMENT;
+    std::memcpy(&m, d->metadata, sizeof m);  // the caller's record may be unaligned
+    if (m.struct_size != sizeof m || m.transport_version != STRIX_TRELLIS_TRANSPORT_VERSION) return STRIX_ERROR_ABI_MISMATCH;
+    uint64_t spare = m.flags;
+    for (const uint64_t word : m.reserved) spare |= word;
+    if (spare) return STRIX_ERROR_INVALID_ARGUMENT;
+    if (m.rows != d->rows || m.columns != d->columns) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    const uint64_t offsets[kRegionCount] = {m.trellis_offset, m.suh_offset, m.svh_offset, m.bias_offset};
+    const uint64_t sizes[kRegionCount] = {m.trellis_bytes, m.suh_bytes, m.svh_bytes, m.bias_bytes};
+    s = geometry_check(m.rows, m.columns, m.bits_x2, enum_bits(m.codebook), m.marker, sizes, g);
     if (s != STRIX_SUCCESS) return s;
-    if (!d->data || !range_ok(d->data, d->data_bytes)) return STRIX_ERROR_INVALID_ARGUMENT;
-    const Region r[4] = {{m.trellis_offset, m.trellis_bytes}, {m.suh_offset, m.suh_bytes},
-                         {m.svh_offset, m.svh_bytes}, {m.bias_offset, m.bias_bytes}};
-    for (int i = 0; i < 4; ++i) {
-        if (r[i].offset > d->data_bytes || r[i].bytes > d->data_bytes - r[i].offset)
-            return STRIX_ERROR_INSUFFICIENT_BUFFER;
-        const uint64_t align = (i == 1 || i == 2) ? 2 : 4;
-        if (r[i].bytes && r[i].offset % align) return STRIX_ERROR_UNSUPPORTED_FORMAT;
-        for (int j = 0; j < i; ++j)
-            if (r[i].bytes && r[j].bytes && r[i].offset < r[j].offset + r[j].bytes &&
-                r[j].offset < r[i].offset + r[i].bytes)
+    if (!g.has_bias && m.bias_offset != 0) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    if (d->data == nullptr || !range_ok(d->data, d->data_bytes)) return STRIX_ERROR_INVALID_ARGUMENT;
+    const unsigned char* base = static_cast<const unsigned char*>(d->data);
+    for (int i = 0; i < kRegionCount; ++i) {
+        if (offsets[i] > d->data_bytes || sizes[i] > d->data_bytes - offsets[i]) return STRIX_ERROR_INSUFFICIENT_BUFFER;
+        if (sizes[i] != 0 && offsets[i] % kRegionRules[i].element_bytes != 0) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+        regions[i].data = sizes[i] != 0 ? base + offsets[i] : nullptr;
+        regions[i].bytes = sizes[i];
+        for (int earlier = 0; earlier < i; ++earlier)
+            if (overlap(regions[i].data, regions[i].bytes, regions[earlier].data, regions[earlier].bytes))
                 return STRIX_ERROR_INVALID_ARGUMENT;
     }
     return STRIX_SUCCESS;
 }
 
-strix_status parts_check(const strix_exl3_parts_desc* d, strix_exl3_metadata_v1& m) {
-    strix_status s = header(d);
+// Separate regions: any host alignment is fine (they are copied byte-wise), pointers and
+// sizes must agree, nothing may wrap the address space, no two regions may share bytes.
+strix_status parts_check(const strix_exl3_parts_desc* d, LayerGeometry& g, strix_host_region (&regions)[kRegionCount]) {
+    const strix_status s = header(d);
     if (s != STRIX_SUCCESS) return s;
     if (d->transport_version != STRIX_TRELLIS_TRANSPORT_VERSION) return STRIX_ERROR_UNSUPPORTED_FORMAT;
-    const strix_host_region r[4] = {d->trellis, d->suh, d->svh, d->bias};
-    for (int i = 0; i < 4; ++i) {
-        if (!r[i].bytes) {
-            if (r[i].data || i != 3) return STRIX_ERROR_INVALID_ARGUMENT;
+    const strix_host_region given[kRegionCount] = {d->trellis, d->suh, d->svh, d->bias};
+    uint64_t sizes[kRegionCount];
+    for (int i = 0; i < kRegionCount; ++i) {
+        regions[i] = given[i];
+        sizes[i] = given[i].bytes;
+        if (given[i].bytes == 0) {
+            if (given[i].data != nullptr || !kRegionRules[i].optional) return STRIX_ERROR_INVALID_ARGUMENT;
             continue;
         }
-        if (!r[i].data || !range_ok(r[i].data, r[i].bytes)) return STRIX_ERROR_INVALID_ARGUMENT;
-        for (int j = 0; j < i; ++j)
-            if (overlap(r[i].data, r[i].bytes, r[j].data, r[j].bytes)) return STRIX_ERROR_INVALID_ARGUMENT;
+        if (given[i].data == nullptr || !range_ok(given[i].data, given[i].bytes)) return STRIX_ERROR_INVALID_ARGUMENT;
+        for (int earlier = 0; earlier < i; ++earlier)
+            if (overlap(given[i].data, given[i].bytes, given[earlier].data, given[earlier].bytes))
+                return STRIX_ERROR_INVALID_ARGUMENT;
     }
-    m = {};
-    m.struct_size = sizeof(m);
-    m.transport_version = d->transport_version;
-    m.rows = d->rows;
-    m.columns = d->columns;
-    m.bits_x2 = d->bits_x2;
-    std::memcpy(&m.codebook, &d->codebook, sizeof(m.codebook));
-    m.marker = d->marker;
-    m.trellis_bytes = d->trellis.bytes;
-    m.suh_bytes = d->suh.bytes;
-    m.svh_bytes = d->svh.bytes;
-    m.bias_bytes = d->bias.bytes;
-    // offsets are meaningless for separate regions; give the blob-equivalent layout
-    uint64_t at = 0;
-    uint64_t* offs[4] = {&m.trellis_offset, &m.suh_offset, &m.svh_offset, &m.bias_offset};
-    for (int i = 0; i < 4; ++i) {
-        if (!r[i].bytes) continue;
-        at = (at + 3) & ~UINT64_C(3);
-        *offs[i] = at;
-        if (r[i].bytes > UINT64_MAX - at) return STRIX_ERROR_UNSUPPORTED_FORMAT;
-        at += r[i].bytes;
-    }
-    return metadata_check(m, d->rows, d->columns);
+    return geometry_check(d->rows, d->columns, d->bits_x2, enum_bits(d->codebook), d->marker, sizes, g);
 }
 
-// One device allocation: [regrouped trellis | suh | svh | bias], 256-byte aligned
-// slices.  The transport-order trellis is staged in a temporary device buffer and
-// regrouped by a kernel; the stream is drained before host ownership returns.
-strix_status prepare_regions(strix_context c, const strix_exl3_metadata_v1& m,
-                             const strix_host_region* regions, cudaStream_t cs, strix_weights* out) {
+// Device memory that is given back unless it is kept.
+struct DeviceBlock {
+    void* p = nullptr;
+    cudaError_t reserve(size_t bytes) { return cudaMalloc(&p, bytes); }
+    void* keep() { void* out = p; p = nullptr; return out; }
+    ~DeviceBlock() { if (p) (void)cudaFree(p); }
+};
+
+// Upload: ONE device allocation [regrouped tiles | suh | svh | bias] with every slice on a
+// 256-byte boundary.  The tiles arrive in transport order in a temporary device buffer and
+// a kernel regroups them; the stream is drained before the call returns, whatever happened,
+// because copies already enqueued still read the caller's host memory.
+strix_status upload_layer(strix_context c, const LayerGeometry& g, const strix_host_region (&regions)[kRegionCount],
+                          cudaStream_t cs, strix_weights* out) {
+    size_t slice[kRegionCount];
+    uint64_t total = 0;
+    for (int i = 0; i < kRegionCount; ++i) {
+        slice[i] = static_cast<size_t>(total);
+        if (regions[i].bytes > SIZE_MAX - total - 2 * kAlign) return STRIX_ERROR_OUT_OF_MEMORY;
+        total = (total + regions[i].bytes + kAlign - 1) / kAlign * kAlign;
+    }
     strix_weights_impl* w = new (std::nothrow) strix_weights_impl;
     if (!w) return STRIX_ERROR_OUT_OF_MEMORY;
-    w->owner = c;
-    w->device.inputs = static_cast<int>(m.columns);
-    w->device.outputs = static_cast<int>(m.rows);
-    w->device.bits = static_cast<int>(m.bits_x2 / 2);
-    w->device.codebook = static_cast<int>(enum_bits(m.codebook));
-    size_t offsets[4];
-    uint64_t total = 0;
-    for (int i = 0; i < 4; ++i) {
-        total = (total + kAlign - 1) & ~(kAlign - 1);
-        offsets[i] = static_cast<size_t>(total);
-        if (regions[i].bytes > SIZE_MAX - total - kAlign) { delete w; return STRIX_ERROR_OUT_OF_MEMORY; }
-        total += regions[i].bytes;
-    }
-    w->allocation_bytes = static_cast<size_t>(total);
-    void* staging = nullptr;
-    cudaError_t e = cudaMalloc(&w->allocation, w->allocation_bytes);
-    if (e == cudaSuccess) e = cudaMalloc(&staging, static_cast<size_t>(regions[0].bytes));
+    DeviceBlock home, staging;
+    cudaError_t e = home.reserve(static_cast<size_t>(total));
+    if (e == cudaSuccess) e = staging.reserve(static_cast<size_t>(regions[kTiles].bytes));
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
-        if (w->allocation) (void)cudaFree(w->allocation);
         delete w;
         return cuda_status(e);
     }
-    unsigned char* base = static_cast<unsigned char*>(w->allocation);
-    w->device.packed = reinterpret_cast<const uint32_t*>(base + offsets[0]);
-    w->device.suh = reinterpret_cast<const uint16_t*>(base + offsets[1]);
-    w->device.svh = reinterpret_cast<const uint16_t*>(base + offsets[2]);
-    w->device.bias = m.bias_bytes ? reinterpret_cast<const float*>(base + offsets[3]) : nullptr;
-    for (int i = 0; i < 4 && e == cudaSuccess; ++i) {
-        if (!regions[i].bytes) continue;
-        void* dst = i == 0 ? staging : static_cast<void*>(base + offsets[i]);
-        e = cudaMemcpyAsync(dst, regions[i].data, static_cast<size_t>(regions[i].bytes),
-                            cudaMemcpyHostToDevice, cs);
+    unsigned char* base = static_cast<unsigned char*>(home.p);
+    for (int i = 0; i < kRegionCount && e == cudaSuccess; ++i) {
+        if (regions[i].bytes == 0) continue;
+        void* target = i == kTiles ? staging.p : base + slice[i];
+        e = cudaMemcpyAsync(target, regions[i].data, static_cast<size_t>(regions[i].bytes), cudaMemcpyHostToDevice, cs);
     }
     if (e == cudaSuccess)
-        e = st::launch_regroup(static_cast<const uint32_t*>(staging),
-                               reinterpret_cast<uint32_t*>(base + offsets[0]), w->device.inputs,
-                               w->device.outputs, w->device.bits, cs);
-    const cudaError_t done = cudaStreamSynchronize(cs);  // also drains earlier uploads on failure
-    (void)cudaFree(staging);
-    if (e != cudaSuccess || done != cudaSuccess) {
-        (void)cudaFree(w->allocation);
+        e = st::launch_regroup(static_cast<const uint32_t*>(staging.p), reinterpret_cast<uint32_t*>(base + slice[kTiles]),
+                               static_cast<int>(g.inputs), static_cast<int>(g.outputs), static_cast<int>(g.bits), cs);
+    const cudaError_t drained = cudaStreamSynchronize(cs);
+    if (e != cudaSuccess || drained != cudaSuccess) {
         delete w;
-        return cuda_status(e != cudaSuccess ? e : done);
+        return cuda_status(e != cudaSuccess ? e : drained);
     }
+    w->owner = c;
+    w->device.packed = reinterpret_cast<const uint32_t*>(base + slice[kTiles]);
+    w->device.suh = reinterpret_cast<const uint16_t*>(base + slice[kInputScales]);
+    w->device.svh = reinterpret_cast<const uint16_t*>(base + slice[kOutputScales]);
+    w->device.bias = g.has_bias ? reinterpret_cast<const float*>(base + slice[kBias]) : nullptr;
+    w->device.inputs = static_cast<int>(g.inputs);
+    w->device.outputs = static_cast<int>(g.outputs);
+    w->device.bits = static_cast<int>(g.bits);
+    w->device.codebook = static_cast<int>(g.codebook);
+    w->allocation = home.keep();
+    w->allocation_bytes = static_cast<size_t>(total);
     ++c->weights_count;
     *out = w;
     return STRIX_SUCCESS;
@@ -273,40 +291,34 @@ strix_status strix_context_destroy(strix_context c) {
     return STRIX_SUCCESS;
 }
 
-strix_status strix_weights_prepare(strix_context c, const strix_exl3_transport_desc* d,
-                                   const strix_stream* stream, strix_weights* out) {
+// Common head of the two preparation entry points: clear the handle, then context and stream.
+static strix_status prepare_begin(strix_context c, const strix_stream* stream, strix_weights* out, cudaStream_t& cs) {
     if (!out) return STRIX_ERROR_INVALID_ARGUMENT;
     *out = nullptr;
-    strix_status s = context_check(c);
-    if (s != STRIX_SUCCESS) return s;
+    const strix_status s = context_check(c);
+    return s != STRIX_SUCCESS ? s : stream_check(c, stream, cs);
+}
+
+strix_status strix_weights_prepare(strix_context c, const strix_exl3_transport_desc* d,
+                                   const strix_stream* stream, strix_weights* out) {
     cudaStream_t cs{};
-    s = stream_check(c, stream, cs);
+    strix_status s = prepare_begin(c, stream, out, cs);
     if (s != STRIX_SUCCESS) return s;
-    strix_exl3_metadata_v1 m{};
-    s = transport_check(d, m);
-    if (s != STRIX_SUCCESS) return s;
-    const unsigned char* base = static_cast<const unsigned char*>(d->data);
-    const strix_host_region r[4] = {{base + m.trellis_offset, m.trellis_bytes},
-                                    {base + m.suh_offset, m.suh_bytes},
-                                    {base + m.svh_offset, m.svh_bytes},
-                                    {m.bias_bytes ? base + m.bias_offset : nullptr, m.bias_bytes}};
-    return prepare_regions(c, m, r, cs, out);
+    LayerGeometry g;
+    strix_host_region regions[kRegionCount];
+    s = blob_check(d, g, regions);
+    return s != STRIX_SUCCESS ? s : upload_layer(c, g, regions, cs, out);
 }
 
 strix_status strix_weights_prepare_parts(strix_context c, const strix_exl3_parts_desc* d,
                                          const strix_stream* stream, strix_weights* out) {
-    if (!out) return STRIX_ERROR_INVALID_ARGUMENT;
-    *out = nullptr;
-    strix_status s = context_check(c);
-    if (s != STRIX_SUCCESS) return s;
     cudaStream_t cs{};
-    s = stream_check(c, stream, cs);
+    strix_status s = prepare_begin(c, stream, out, cs);
     if (s != STRIX_SUCCESS) return s;
-    strix_exl3_metadata_v1 m{};
-    s = parts_check(d, m);
-    if (s != STRIX_SUCCESS) return s;
-    const strix_host_region r[4] = {d->trellis, d->suh, d->svh, d->bias};
-    return prepare_regions(c, m, r, cs, out);
+    LayerGeometry g;
+    strix_host_region regions[kRegionCount];
+    s = parts_check(d, g, regions);
+    return s != STRIX_SUCCESS ? s : upload_layer(c, g, regions, cs, out);
 }
 
 strix_status strix_weights_destroy(strix_weights w) {

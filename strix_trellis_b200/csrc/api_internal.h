@@ -35,37 +35,56 @@ namespace sapi {
 
 constexpr uint64_t kAlign = STRIX_TRELLIS_WORKSPACE_ALIGNMENT;
 
-template <class E> inline uint32_t enum_bits(const E& value) {
-    static_assert(sizeof(E) == sizeof(uint32_t), "enum ABI");
-    uint32_t raw;
-    std::memcpy(&raw, &value, sizeof raw);  // never load an out-of-range C enum
-    return raw;
+// ---- small vocabulary of the validation code ---------------------------------------------
+// An enum field of a descriptor is whatever 32 bits the caller stored there; it is compared as
+// a word and never loaded as the enum type.
+template <class E> inline uint32_t enum_bits(const E& field) {
+    static_assert(sizeof(E) == 4, "descriptor enums are 32-bit words");
+    uint32_t word = 0;
+    std::memcpy(&word, &field, 4);
+    return word;
 }
-template <class T> inline strix_status header(const T* d) {
-    if (!d) return STRIX_ERROR_INVALID_ARGUMENT;
-    if (d->struct_size != sizeof(T) || d->abi_version != STRIX_TRELLIS_ABI_VERSION)
-        return STRIX_ERROR_ABI_MISMATCH;
-    for (uint64_t v : d->reserved)
-        if (v) return STRIX_ERROR_INVALID_ARGUMENT;
-    return STRIX_SUCCESS;
+
+// Every versioned descriptor starts with {struct_size, abi_version} and ends with a `reserved`
+// array.  Order of the verdicts: missing -> invalid argument, wrong size or version -> ABI
+// mismatch, non-zero reserved word -> invalid argument.
+template <class D> inline strix_status header(const D* desc) {
+    if (desc == nullptr) return STRIX_ERROR_INVALID_ARGUMENT;
+    const bool same_abi = desc->struct_size == sizeof(D) && desc->abi_version == STRIX_TRELLIS_ABI_VERSION;
+    if (!same_abi) return STRIX_ERROR_ABI_MISMATCH;
+    uint64_t any = 0;
+    for (const uint64_t word : desc->reserved) any |= word;
+    return any ? STRIX_ERROR_INVALID_ARGUMENT : STRIX_SUCCESS;
 }
+
 inline strix_status cuda_status(cudaError_t e) {
-    if (e == cudaSuccess) return STRIX_SUCCESS;
-    return e == cudaErrorMemoryAllocation ? STRIX_ERROR_OUT_OF_MEMORY : STRIX_ERROR_BACKEND;
+    switch (e) {
+    case cudaSuccess: return STRIX_SUCCESS;
+    case cudaErrorMemoryAllocation: return STRIX_ERROR_OUT_OF_MEMORY;
+    default: return STRIX_ERROR_BACKEND;
+    }
 }
-inline bool mul_ok(uint64_t a, uint64_t b, uint64_t& out) {
-    if (b && a > UINT64_MAX / b) return false;
-    out = a * b;
-    return true;
+
+// a * b without wrap-around
+inline bool mul_ok(uint64_t a, uint64_t b, uint64_t& product) {
+    return !__builtin_mul_overflow(a, b, &product);
 }
-inline bool range_ok(const void* p, uint64_t bytes) {
-    return bytes <= SIZE_MAX && bytes <= UINTPTR_MAX - reinterpret_cast<uintptr_t>(p);
-}
-inline bool overlap(const void* a, uint64_t an, const void* b, uint64_t bn) {
-    if (!an || !bn) return false;
-    const uintptr_t x = reinterpret_cast<uintptr_t>(a), y = reinterpret_cast<uintptr_t>(b);
-    return x < y + bn && y < x + an;
-}
+
+// A byte span of the caller's address space.  `fits()` says that begin + bytes neither wraps
+// the address space nor exceeds size_t; two spans `touch()` when both are non-empty and share
+// at least one byte.
+struct Span {
+    uintptr_t begin;
+    uint64_t bytes;
+    Span(const void* p, uint64_t n) : begin(reinterpret_cast<uintptr_t>(p)), bytes(n) {}
+    bool fits() const { return bytes <= SIZE_MAX && bytes <= UINTPTR_MAX - begin; }
+    bool touch(const Span& o) const {
+        if (bytes == 0 || o.bytes == 0) return false;
+        return begin < o.begin ? o.begin - begin < bytes : begin - o.begin < o.bytes;
+    }
+};
+inline bool range_ok(const void* p, uint64_t bytes) { return Span(p, bytes).fits(); }
+inline bool overlap(const void* a, uint64_t an, const void* b, uint64_t bn) { return Span(a, an).touch(Span(b, bn)); }
 
 strix_status context_check(strix_context c);
 strix_status stream_check(strix_context c, const strix_stream* s, cudaStream_t& out);
