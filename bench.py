@@ -211,7 +211,9 @@ def moe_case(torch, ctx, stream, tokens_list, experts=32, top_k=8, model=4096, i
     """Routed-expert block of benchmark configuration 5 on one rank's bank of `experts`
     experts (K2 gate/up/down, 201 MB of packed weights), device-routed.  Routes rotate over
     four seeded sets between submits (one small device copy, inside the timed region) so that
-    successive submits read different experts.  Microseconds per submit."""
+    successive submits read different experts.  Microseconds per submit and GB/s over the packed
+    bytes of the DISTINCT experts a submit touches (an expert's weights are read once per eight
+    rows routed to it)."""
     from strix_trellis_b200 import synthetic
     from strix_trellis_b200.runtime import MoePlan
     proto = [synthetic.make_layer(model, inter, bits, seed=synthetic.BASE_SEED + 500, sigma=0.5),
@@ -236,8 +238,10 @@ def moe_case(torch, ctx, stream, tokens_list, experts=32, top_k=8, model=4096, i
             sc_d.copy_(sc_all[turn[0]])
             plan.submit()
         us = time_calls(torch, stream, submit, reps)
-        routed = t * top_k * sum(l.packed_bytes for l in proto)
-        out[f"T{t}"] = {"us": round(us, 1), "GBps_over_routed_weight_bytes": round(routed / us / 1e3, 1)}
+        distinct = float(np.mean([len(np.unique(i)) for i, _ in sets]))
+        unique_bytes = distinct * sum(l.packed_bytes for l in proto)
+        out[f"T{t}"] = {"us": round(us, 1), "distinct_experts": round(distinct, 1),
+                        "GBps_over_distinct_expert_bytes": round(unique_bytes / us / 1e3, 1)}
         plan.close()
     for e in bank:
         for w in e:
@@ -245,11 +249,53 @@ def moe_case(torch, ctx, stream, tokens_list, experts=32, top_k=8, model=4096, i
     return out
 
 
-def tp_case(torch, dist, ctx, stream, rank, world, rows_list=(1, 4, 8), reps=24):
-    """Benchmark configuration 4 at `world` ranks: (a) row-parallel 16384 -> 4096 K5 with
-    all-reduce, (b) LM head 4096 -> 129280 K5 with all-gather.  Each rank generates only its
-    own shard and rotates over enough device copies of it to exceed L2 twice.  Microseconds
-    per call (local kernel + collective) and for the local kernel alone, max over ranks."""
+def _gates(got, want, what, nrmse_bound=3e-5):
+    """The reference's acceptance criterion (docs/GPU_TESTS.md:126-131); returns the two figures."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    if not np.isfinite(got).all():
+        raise SystemExit(f"{what}: non-finite output")
+    err = np.abs(got - want)
+    maxabs = float(err.max())
+    nrmse = float(np.sqrt((err ** 2).sum() / max((want ** 2).sum(), 1e-30)))
+    if maxabs > 5e-4 * max(1.0, float(np.abs(want).max())) or nrmse > nrmse_bound:
+        raise SystemExit(f"{what}: parity check failed before timing (maxabs {maxabs:.3e}, NRMSE {nrmse:.3e})")
+    return maxabs, nrmse
+
+
+def _graph_us(torch, stream, calls, replays=6):
+    """`calls` (a list of thunks, each a fixed sequence of kernel launches) captured into one
+    CUDA graph; device time per call in microseconds over `replays` replays."""
+    with torch.cuda.stream(stream):
+        for c in calls:
+            c()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for c in calls:
+                c()
+        graph.replay()
+        stream.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(replays):
+            graph.replay()
+        b.record(stream)
+        stream.synchronize()
+    return a.elapsed_time(b) * 1e3 / (replays * len(calls)), graph
+
+
+def tp_case(torch, dist, ctx, stream, rank, world, rows_list=(1, 4, 8)):
+    """Benchmark configuration 4 at `world` ranks: (a) row-parallel 16384 -> 4096 K5, rank outputs
+    summed over the ranks, (b) LM head 4096 -> 129280 K5, rank blocks concatenated.  Each rank
+    generates only its own shard and rotates over enough device copies of it to exceed L2 twice.
+    Before timing every rank checks its result against the CPU contract: the sum of the ranks'
+    shard outputs (each rank evaluates its own shard on the CPU, the references are added in
+    float64 across ranks), its own block of the logits (first sixteen H128 blocks), and the bytes
+    of every other rank's block against a hash taken where the block was computed.  Microseconds
+    per call (local kernel + exchange, all copies in one CUDA graph) and for the local kernel
+    alone, max over ranks."""
+    import hashlib
+    from oracle import c_oracle
     from strix_trellis_b200 import synthetic, tp
     from strix_trellis_b200.container import Exl3Tensor
     from strix_trellis_b200.tp_runtime import ColumnParallelLinear, RowParallelLinear
@@ -259,35 +305,66 @@ def tp_case(torch, dist, ctx, stream, rank, world, rows_list=(1, 4, 8), reps=24)
         return Exl3Tensor(layer.trellis, layer.suh, layer.svh, 5.0, layer.codebook, None, "synthetic", "w"), layer
 
     a0, a1 = tp.h128_bounds(16384, world)[rank]
-    b0, b1 = tp.h128_bounds(129280, world)[rank]
+    bounds = tp.h128_bounds(129280, world)
+    b0, b1 = bounds[rank]
     row_t, row_l = shard_layer(a1 - a0, 4096, synthetic.BASE_SEED + 600)
     col_t, col_l = shard_layer(4096, b1 - b0, synthetic.BASE_SEED + 700)
     need = 256 * 1024 * 1024
-    rows_ = [RowParallelLinear(ctx, row_t, rank, world, full_inputs=16384)
-             for _ in range(-(-need // row_l.packed_bytes))]
-    cols_ = [ColumnParallelLinear(ctx, col_t, rank, world, full_outputs=129280)
-             for _ in range(-(-need // col_l.packed_bytes))]
-    out = {"row_parallel_copies": len(rows_), "lm_head_copies": len(cols_)}
+    with torch.cuda.stream(stream):
+        rows_ = [RowParallelLinear(ctx, row_t, rank, world, full_inputs=16384)
+                 for _ in range(-(-need // row_l.packed_bytes))]
+        cols_ = [ColumnParallelLinear(ctx, col_t, rank, world, full_outputs=129280)
+                 for _ in range(-(-need // col_l.packed_bytes))]
+    out = {"row_parallel_copies": len(rows_), "lm_head_copies": len(cols_), "parity_checked": True}
+    worst = {"row_parallel": [0.0, 0.0], "lm_head": [0.0, 0.0]}
     for r in rows_list:
-        x_row = torch.from_numpy(synthetic.make_activations(r, 16384, seed=synthetic.BASE_SEED + 601)).cuda()
-        y_row = torch.empty((r, 4096), dtype=torch.float32, device="cuda")
-        x_col = torch.from_numpy(synthetic.make_activations(r, 4096, seed=synthetic.BASE_SEED + 701)).cuda()
-        turn = [0]
-
-        def pick(pool):
-            turn[0] += 1
-            return pool[turn[0] % len(pool)]
-        wr, wc = max(3, len(rows_)), max(3, len(cols_))  # warm-up freezes every copy's plan
-        us = [time_calls(torch, stream, lambda: pick(rows_).forward(x_row, y_row), reps, wr),
-              time_calls(torch, stream, lambda: pick(rows_).local(x_row, y_row), reps, wr),
-              time_calls(torch, stream, lambda: pick(cols_).forward(x_col), reps, wc),
-              time_calls(torch, stream, lambda: pick(cols_).local(x_col), reps, wc)]
+        x_row_h = synthetic.make_activations(r, 16384, seed=synthetic.BASE_SEED + 601)
+        x_col_h = synthetic.make_activations(r, 4096, seed=synthetic.BASE_SEED + 701)
+        x_row, x_col = torch.from_numpy(x_row_h).cuda(), torch.from_numpy(x_col_h).cuda()
+        ys = [torch.empty((r, 4096), dtype=torch.float32, device="cuda") for _ in rows_]
+        # ---- parity before timing (first copy; the other copies hold the same bytes) ----
+        with torch.cuda.stream(stream):
+            got_row = rows_[0].forward(x_row, ys[0]).cpu().numpy()
+            got_col_t = cols_[0].forward(x_col)
+            got_col = got_col_t.cpu().numpy()
+            local_block = cols_[0].local(x_col).cpu().numpy()
+        want = c_oracle.linear(row_l.trellis, row_l.suh, row_l.svh, None, 5, 2,
+                               np.ascontiguousarray(x_row_h[:, a0:a1])).astype(np.float64)
+        want_t = torch.from_numpy(want).cuda()
+        if world > 1:
+            dist.all_reduce(want_t)
+        m = _gates(got_row, want_t.cpu().numpy(), f"row-parallel sum, rank {rank}, rows {r}")
+        worst["row_parallel"] = [max(a, b) for a, b in zip(worst["row_parallel"], m)]
+        head = min(2048, b1 - b0)
+        want_head = c_oracle.linear(np.ascontiguousarray(col_l.trellis[:, :head // 16]), col_l.suh, col_l.svh[:head],
+                                    None, 5, 2, x_col_h)
+        m = _gates(got_col[:, b0:b0 + head], want_head, f"LM head block, rank {rank}, rows {r}")
+        worst["lm_head"] = [max(a, b) for a, b in zip(worst["lm_head"], m)]
+        digests = [hashlib.sha256(local_block.tobytes()).hexdigest()]
+        if world > 1:
+            digests = [None] * world
+            dist.all_gather_object(digests, hashlib.sha256(local_block.tobytes()).hexdigest())
+        for q, (c0, c1) in enumerate(bounds):
+            if hashlib.sha256(np.ascontiguousarray(got_col[:, c0:c1]).tobytes()).hexdigest() != digests[q]:
+                raise SystemExit(f"LM head: block of rank {q} arrived with different bytes on rank {rank}")
+        # ---- timing: every copy once per graph replay ----
+        us = [_graph_us(torch, stream, [lambda l=l, y=y: l.forward(x_row, y) for l, y in zip(rows_, ys)])[0],
+              _graph_us(torch, stream, [lambda l=l, y=y: l.local(x_row, y) for l, y in zip(rows_, ys)])[0],
+              _graph_us(torch, stream, [lambda l=l: l.forward(x_col) for l in cols_])[0],
+              _graph_us(torch, stream, [lambda l=l: l.local(x_col) for l in cols_])[0]]
         t = torch.tensor(us, device="cuda")
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         us = [round(float(v), 1) for v in t.tolist()]
         out[f"R{r}"] = {"row_parallel_us": us[0], "row_parallel_kernel_us": us[1],
                         "lm_head_us": us[2], "lm_head_kernel_us": us[3]}
+    w = torch.tensor(worst["row_parallel"] + worst["lm_head"], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(w, op=dist.ReduceOp.MAX)
+    out["worst_maxabs_nrmse"] = {"row_parallel": [float(f"{v:.3e}") for v in w[:2].tolist()],
+                                 "lm_head": [float(f"{v:.3e}") for v in w[2:].tolist()]}
+    if world > 1:
+        dist.barrier()
     for layer in rows_ + cols_:
         layer.close()
     return out
@@ -296,11 +373,14 @@ def tp_case(torch, dist, ctx, stream, rank, world, rows_list=(1, 4, 8), reps=24)
 def ep_case(torch, dist, ctx, stream, rank, world, tokens_list=(1, 8, 64), experts=256, top_k=8, model=4096,
             inter=2048, bits=2, reps=6):
     """Benchmark configuration 5: 256 experts owned contiguously by the ranks, top-8 routing,
-    K2 gate/up/down; tokens live round-robin on the ranks; all-to-all dispatch of routed rows
-    to the owners, expert kernels, all-to-all back, combine at the home rank in slot order.
-    Microseconds per forward (device time between events on rank-local streams, max over
-    ranks; fixed-capacity exchange, no host synchronisation inside a forward).  Routes rotate over four
-    seeded sets so that successive forwards touch different experts."""
+    K2 gate/up/down; tokens live rank-major on the ranks.  A step is two exchanges through
+    peer memory around the expert kernels and the combine at the home rank in slot order.
+    Every expert holds the same three seeded layers (distinct device copies), so before timing each
+    rank checks its own tokens against the CPU contract evaluated with those layers (up to two
+    tokens per rank).  Microseconds per step: the captured graph of one step replayed (device time,
+    max over ranks) and the same step enqueued call by call.  Routes rotate over four seeded sets so
+    that successive steps touch different experts."""
+    from oracle import c_oracle
     from strix_trellis_b200 import synthetic
     from strix_trellis_b200.tp_runtime import ExpertParallelMoE
     proto = [synthetic.make_layer(model, inter, bits, seed=synthetic.BASE_SEED + 500, sigma=0.5),
@@ -309,33 +389,56 @@ def ep_case(torch, dist, ctx, stream, rank, world, tokens_list=(1, 8, 64), exper
     per = -(-experts // world)
     mine = range(rank * per, min(experts, (rank + 1) * per))
     bank = [tuple(ctx.prepare(l) for l in proto) for _ in mine]
-    out = {}
+    out = {"parity_checked": True}
+    worst = [0.0, 0.0]
+
+    def lin(layer, v):
+        return c_oracle.linear(layer.trellis, layer.suh, layer.svh, None, bits, 2, v)
+
     with torch.cuda.stream(stream):
         for t in tokens_list:
             sets = [synthetic.make_routes(t, experts, top_k, seed=synthetic.BASE_SEED + 520 + k) for k in range(4)]
             x = synthetic.make_activations(t, model, seed=synthetic.BASE_SEED + 503)
-            home = [i for i in range(t) if i % world == rank]
+            slots = -(-t // world)
+            home = list(range(rank * slots, min(t, (rank + 1) * slots)))
             xh = torch.from_numpy(x[home]).cuda() if home else torch.zeros((0, model), device="cuda")
-            ep = ExpertParallelMoE(ctx, bank, experts, rank, world, model, max_tokens=-(-t // world), top_k=top_k)
+            ep = ExpertParallelMoE(ctx, bank, experts, rank, world, model, max_tokens=slots, top_k=top_k)
             on_device = [(torch.from_numpy(ids[home].astype(np.int64).reshape(len(home), top_k)).cuda(),
                           torch.from_numpy(scores[home].reshape(len(home), top_k)).cuda()) for ids, scores in sets]
+            # ---- parity before timing ----
+            got = ep.forward(xh, *on_device[0]).cpu().numpy()
+            for j, token in enumerate(home[:2]):
+                hidden = c_oracle.swiglu(lin(proto[0], x[token:token + 1]), lin(proto[1], x[token:token + 1]))
+                down = lin(proto[2], hidden)[0]
+                want = np.zeros(model, np.float32)
+                for sc in sets[0][1][token]:  # ascending slot order from +0; every expert holds the same layers
+                    if sc != 0.0:
+                        want = want + np.float32(sc) * down
+                m = _gates(got[j], want, f"expert-parallel block, token {token}, {t} tokens, rank {rank}", 2.5e-4)
+                worst = [max(a, b) for a, b in zip(worst, m)]
+            # ---- timing ----
+            run = ep.capture(len(home))
             turn = [0]
 
-            run = ep.capture(len(home)) if world == 1 else ep.forward  # one rank: the forward is one graph
-
-            def forward():
+            def step(fn):
                 turn[0] = (turn[0] + 1) % 4
-                return run(xh, *on_device[turn[0]])
-            # more than one rank: the first all-to-alls also set up NCCL's peer connections
-            us = time_calls(torch, stream, forward, reps if world == 1 else 2 * reps, warm=2 if world == 1 else 6)
-            tt = torch.tensor([us], device="cuda")
+                return fn(xh, *on_device[turn[0]])
+            us_graph = time_calls(torch, stream, lambda: step(run), reps if world == 1 else 2 * reps, warm=3)
+            us_eager = time_calls(torch, stream, lambda: step(ep.forward), reps if world == 1 else 2 * reps, warm=3)
+            tt = torch.tensor([us_graph, us_eager], device="cuda")
             if world > 1:
                 dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            out[f"T{t}"] = {"us": round(float(tt.item()), 1)}
+            out[f"T{t}"] = {"us": round(float(tt[0].item()), 1), "us_call_by_call": round(float(tt[1].item()), 1)}
+            if world > 1:
+                dist.barrier()
             ep.close()
+    w = torch.tensor(worst, device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(w, op=dist.ReduceOp.MAX)
+    out["worst_maxabs_nrmse"] = [float(f"{v:.3e}") for v in w.tolist()]
     for e in bank:
-        for w in e:
-            w.close()
+        for w_ in e:
+            w_.close()
     return out
 
 

@@ -62,7 +62,8 @@ strix_status strix_b200_gemv_partition(uint64_t inputs, uint64_t outputs, uint32
 
 /* Reads and clears the context's device status word.  Non-zero means that a bounded
  * wait inside a kernel gave up (bit 0 weight ring full-wait, bit 1 empty-wait, bit 2
- * drain at exit, bit 3 tensor pipeline, bit 4 split-K fold); results of that launch are invalid,
+ * drain at exit, bit 3 tensor pipeline, bit 4 split-K fold, bit 5 a peer exchange that never
+ * completed); results of that launch are invalid,
  * and after bit 4 the plan whose launch it was should be recreated (its fold scratch may hold
  * words of the abandoned launch; direct strix_gemv calls reset their scratch on every call).
  * Synchronises the device.  No counterpart in the reference (its kernels never wait). */
@@ -87,6 +88,123 @@ strix_status strix_b200_moe_combine(strix_context context, const float *rows, co
                                     uint32_t tokens, uint32_t top_k, uint32_t width, float *y,
                                     uint64_t y_stride, float alpha, float beta,
                                     const strix_stream *stream);
+
+/* The combine above with a per-token validity mask: a token whose row_valid entry is zero gets
+ * a NaN row (the reference's answer to an invalid device route, src/tp_moe.hip:131-138).
+ * row_valid may be NULL (all rows valid). */
+strix_status strix_b200_moe_combine_rows(strix_context context, const float *rows, const float *scores,
+                                         const int32_t *row_valid, uint32_t tokens, uint32_t top_k,
+                                         uint32_t width, float *y, uint64_t y_stride, float alpha,
+                                         float beta, const strix_stream *stream);
+
+/* ---- expert parallelism ------------------------------------------------------------------
+ * A device-routed plan's bank as a window of the router's id space: route id g is bank entry
+ * g - first_expert when that is inside the bank, lives on another rank when g < experts_total
+ * (its slot runs nothing here and does not invalidate the row), and invalidates the row
+ * otherwise.  After this call strix_tp_moe_plan_submit yields this rank's contribution (the
+ * sum over its own experts' slots, the reference's per-rank semantics,
+ * include/strix_trellis.h:215-216); the default window is the whole bank.  Every rank applies
+ * the same row rules (ids in range and distinct, scores finite and non-negative), so all ranks
+ * agree on which rows are valid.  No counterpart as an entry point in the reference. */
+strix_status strix_b200_moe_plan_set_window(strix_tp_moe_plan plan, uint32_t first_expert,
+                                            uint32_t experts_total);
+/* Routing, gate/up, SwiGLU and down projections of the routes this rank owns, without the
+ * combine: the per-route output rows stay in plan memory for an exchange to carry home. */
+strix_status strix_b200_moe_plan_projections(strix_tp_moe_plan plan);
+/* Where those rows are: each = F32 [tokens * top_k][model] (rows of routes owned elsewhere are
+ * not written), row_valid = int32 [tokens] (device-routed plans; NULL otherwise). */
+strix_status strix_b200_moe_plan_rows(strix_tp_moe_plan plan, const float **each,
+                                      const int32_t **row_valid);
+
+/* ---- exchange between the ranks of one node through peer memory over NVLink -----------------
+ * The shard-boundary steps of the tensor- and expert-parallel layers as single kernels that
+ * store straight into the other ranks' memory: no library collective, no host
+ * synchronisation, capturable into a CUDA graph.  The reference has no inter-rank
+ * communication (README.md:773); it only fixes the arithmetic of these steps
+ * (docs/TP_RANK.md:150-156).
+ *
+ * Every rank creates an ARENA and publishes its 64-byte handle to the other ranks (any host
+ * channel); a GROUP maps all arenas of the node.  The first STRIX_B200_PEER_CONTROL_BYTES of
+ * an arena belong to the library; the caller assigns the rest as REGIONS (byte offsets,
+ * multiples of 256) to the exchanges it runs.  A region holds two copies of an exchange's
+ * payload, used alternately, so a layer may run back to back.  All ranks must issue the same
+ * sequence of exchanges on a group.  A rank that never shows up makes the others give up after
+ * about a second: bit 5 of the status word (strix_b200_device_status) is set and the result of
+ * that exchange is invalid.  `local_count` consecutive ranks starting at `first_rank` may live
+ * in this process on this device: per-rank arguments are then arrays of `local_count` entries
+ * (one entry in production). */
+#define STRIX_B200_PEER_MAX_RANKS 8
+#define STRIX_B200_PEER_HANDLE_BYTES 64
+#define STRIX_B200_PEER_CONTROL_BYTES UINT64_C(2304)
+typedef struct strix_b200_peer_group_impl *strix_b200_peer_group;
+
+strix_status strix_b200_peer_arena_create(strix_context context, uint64_t bytes, void **arena,
+                                          unsigned char *handle /* [64] */);
+strix_status strix_b200_peer_arena_destroy(strix_context context, void *arena);
+/* handles: world x 64 bytes in rank order (entries of local ranks are ignored; may be NULL
+ * when every rank is local). */
+strix_status strix_b200_peer_group_create(strix_context context, void *const *local_arenas,
+                                          uint32_t local_count, uint32_t first_rank,
+                                          uint64_t arena_bytes, const unsigned char *handles,
+                                          uint32_t world, strix_b200_peer_group *out);
+strix_status strix_b200_peer_group_destroy(strix_b200_peer_group group);
+
+/* rows[i] (count floats, count % 4 == 0, 16-byte aligned) of every rank is replaced by the sum
+ * over ranks, added in ascending rank order from +0: identical bits on every rank.  Region
+ * size: 2 * world * count * 4 bytes. */
+strix_status strix_b200_peer_sum(strix_b200_peer_group group, float *const *rows, uint64_t count,
+                                 uint64_t region, const strix_stream *stream);
+
+/* Every rank's block into one matrix on every rank; up to three matrices of 32-bit words
+ * travel in one exchange.  Rank r contributes rows[r] x width[r] words (contiguous) placed at
+ * (row_at[r], col_at[r]) of the total_rows x total_cols result (total_rows = max row_at+rows).
+ * result[i] != NULL receives a private contiguous copy; with NULL the result is read in the
+ * arena at region + parity * total_rows * total_cols * 4.  Region size per matrix:
+ * 2 * total_rows * total_cols * 4 bytes. */
+typedef struct strix_b200_peer_matrix {
+    const void *block[STRIX_B200_PEER_MAX_RANKS];  /* per local rank */
+    void *result[STRIX_B200_PEER_MAX_RANKS];       /* per local rank, or NULL */
+    uint32_t width[STRIX_B200_PEER_MAX_RANKS];     /* per rank, 32-bit words */
+    uint32_t col_at[STRIX_B200_PEER_MAX_RANKS];    /* per rank */
+    uint64_t total_cols;
+    uint64_t region;
+} strix_b200_peer_matrix;
+typedef struct strix_b200_peer_gather_desc {
+    uint32_t struct_size;
+    uint32_t abi_version;
+    uint32_t matrices; /* 1..3 */
+    uint32_t flags;    /* zero */
+    uint32_t rows[STRIX_B200_PEER_MAX_RANKS];   /* per rank */
+    uint32_t row_at[STRIX_B200_PEER_MAX_RANKS]; /* per rank */
+    strix_b200_peer_matrix matrix[3];
+    uint64_t reserved[2];
+} strix_b200_peer_gather_desc;
+strix_status strix_b200_peer_gather(strix_b200_peer_group group, const strix_b200_peer_gather_desc *desc,
+                                    const strix_stream *stream);
+
+/* Routed rows back to the home rank of their token.  Tokens are laid out rank-major (token t
+ * lives on rank t / tokens_per_rank).  A rank stores the row of route (t, s) when row_valid[t]
+ * is non-zero and ids[t, s] lies in its window; it lands at row (t % tokens_per_rank) * top_k + s
+ * of the home rank's region (2 * tokens_per_rank * top_k * width * 4 bytes, parity as above). */
+typedef struct strix_b200_peer_return_desc {
+    uint32_t struct_size;
+    uint32_t abi_version;
+    const float *each[STRIX_B200_PEER_MAX_RANKS];       /* per local rank: [tokens * top_k][width] */
+    const uint32_t *ids[STRIX_B200_PEER_MAX_RANKS];     /* per local rank: [tokens][top_k] */
+    const int32_t *row_valid[STRIX_B200_PEER_MAX_RANKS];/* per local rank: [tokens] */
+    uint32_t first_expert[STRIX_B200_PEER_MAX_RANKS];   /* per local rank */
+    uint32_t experts[STRIX_B200_PEER_MAX_RANKS];        /* per local rank */
+    uint32_t tokens;
+    uint32_t tokens_per_rank;
+    uint32_t top_k;
+    uint32_t flags; /* zero */
+    uint64_t width; /* floats per row, multiple of 4 */
+    uint64_t region;
+    uint64_t reserved[2];
+} strix_b200_peer_return_desc;
+strix_status strix_b200_peer_return_routes(strix_b200_peer_group group,
+                                           const strix_b200_peer_return_desc *desc,
+                                           const strix_stream *stream);
 
 /* strix_gemv for callers that may not allocate.  It has no counterpart in the reference.
  *

@@ -83,9 +83,10 @@ strix_status strix_b200_gemv_splits(strix_context c, strix_weights w, uint32_t r
     return STRIX_SUCCESS;
 }
 
-strix_status strix_b200_moe_combine(strix_context c, const float* rows, const float* scores, uint32_t tokens,
-                                    uint32_t top_k, uint32_t width, float* y, uint64_t y_stride, float alpha,
-                                    float beta, const strix_stream* stream) {
+strix_status strix_b200_moe_combine_rows(strix_context c, const float* rows, const float* scores,
+                                         const int32_t* row_valid, uint32_t tokens, uint32_t top_k, uint32_t width,
+                                         float* y, uint64_t y_stride, float alpha, float beta,
+                                         const strix_stream* stream) {
     strix_status s = context_check(c);
     if (s != STRIX_SUCCESS) return s;
     // Stream and pointer provenance are inspected with runtime / driver queries, which a
@@ -114,12 +115,19 @@ strix_status strix_b200_moe_combine(strix_context c, const float* rows, const fl
         s = device_buffer(c, rows, n_rows, 4);
         if (s == STRIX_SUCCESS) s = device_buffer(c, scores, n_scores, 4);
         if (s == STRIX_SUCCESS) s = device_buffer(c, y, n_y, 4);
+        if (s == STRIX_SUCCESS && row_valid) s = device_buffer(c, row_valid, (uint64_t)tokens * 4, 4);
         if (s != STRIX_SUCCESS) return s;
     } else if (!rows || !scores || !y) {
         return STRIX_ERROR_INVALID_ARGUMENT;
     }
-    return cuda_status(st::launch_moe_combine(rows, scores, nullptr, (int)tokens, (int)top_k, (int)width, y,
+    return cuda_status(st::launch_moe_combine(rows, scores, row_valid, (int)tokens, (int)top_k, (int)width, y,
                                               (long long)y_stride, alpha, beta, cs));
+}
+
+strix_status strix_b200_moe_combine(strix_context c, const float* rows, const float* scores, uint32_t tokens,
+                                    uint32_t top_k, uint32_t width, float* y, uint64_t y_stride, float alpha,
+                                    float beta, const strix_stream* stream) {
+    return strix_b200_moe_combine_rows(c, rows, scores, nullptr, tokens, top_k, width, y, y_stride, alpha, beta, stream);
 }
 
 // Pure host arithmetic: no context, no device.

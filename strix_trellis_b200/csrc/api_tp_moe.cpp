@@ -32,6 +32,7 @@ struct strix_tp_moe_plan_impl {
     float* y = nullptr;
     long long y_stride = 0;
     float alpha = 1.f, beta = 0.f;
+    st::MoeWindow window{0, 0};  // device-routed plans: where the bank sits in the router's id space
 };
 
 // A dense pair-style plan with SwiGLU: two grouped problems + the activation.
@@ -242,8 +243,8 @@ strix_status host_routing(const strix_tp_moe_desc* d, int tokens, int top_k, std
 strix_status enqueue_gate_up(strix_tp_moe_plan_impl* p) {
     cudaError_t e = cudaSuccess;
     if (p->device_routed)
-        e = st::launch_moe_route(p->route_ids, p->scores, p->tokens, p->top_k, p->bank, p->bank_count, p->gu, p->down,
-                                 p->row_valid, p->stream);
+        e = st::launch_moe_route(p->route_ids, p->scores, p->tokens, p->top_k, p->bank, p->bank_count, p->window, p->gu,
+                                 p->down, p->row_valid, p->stream);
     if (e == cudaSuccess)
         e = st::launch_grouped(p->gu, p->gu_count, p->model, p->inter, p->codebook, p->gu_plan, p->owner->status,
                                p->owner->programmatic_launch, p->stream);
@@ -252,12 +253,15 @@ strix_status enqueue_gate_up(strix_tp_moe_plan_impl* p) {
     return cuda_status(e);
 }
 
-strix_status enqueue_down(strix_tp_moe_plan_impl* p) {
+strix_status enqueue_down(strix_tp_moe_plan_impl* p, bool combine = true) {
     cudaError_t e = st::launch_grouped(p->down, p->down_count, p->inter, p->model, p->codebook, p->down_plan,
                                        p->owner->status, p->owner->programmatic_launch, p->stream);
-    if (e == cudaSuccess)
+    if (e == cudaSuccess && combine) {
+        const bool partial = p->device_routed && p->window.experts_total != p->bank_count;  // other ranks own some slots
         e = st::launch_moe_combine(p->each, p->scores, p->device_routed ? p->row_valid : nullptr, p->tokens, p->top_k,
-                                   p->model, p->y, p->y_stride, p->alpha, p->beta, p->stream);
+                                   p->model, p->y, p->y_stride, p->alpha, p->beta, p->stream,
+                                   partial ? p->route_ids : nullptr, p->window.first_expert, p->bank_count);
+    }
     return cuda_status(e);
 }
 
@@ -404,6 +408,7 @@ strix_status create_device(strix_context c, const strix_tp_moe_device_desc* d, c
     p->gu_count = 2 * routes;
     p->down_count = routes;
     p->bank_count = (int)d->expert_count;
+    p->window = st::MoeWindow{0, p->bank_count};
     p->gu_plan = st::plan_grouped(g.model, g.inter, g.max_bits, p->gu_count, c->sm_count);
     p->down_plan = st::plan_grouped(g.inter, g.model, g.max_bits, p->down_count, c->sm_count);
     const size_t bytes = layout_block(p, p->gu_count, p->down_count, false);
@@ -523,6 +528,31 @@ strix_status strix_tp_moe_plan_submit(strix_tp_moe_plan p) {
     if (s == STRIX_SUCCESS) s = enqueue_down(p);
     return s;
 }
+// ---- expert parallelism: the bank as a window of the router's id space ------------------------
+strix_status strix_b200_moe_plan_set_window(strix_tp_moe_plan p, uint32_t first_expert, uint32_t experts_total) {
+    if (!p || !p->device_routed) return STRIX_ERROR_INVALID_ARGUMENT;
+    if (experts_total > INT_MAX || (uint64_t)first_expert + (uint64_t)p->bank_count > experts_total)
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    p->window = st::MoeWindow{(int)first_expert, (int)experts_total};
+    return STRIX_SUCCESS;
+}
+// Routing, gate/up, SwiGLU and down of the routes this rank owns; no combine.
+strix_status strix_b200_moe_plan_projections(strix_tp_moe_plan p) {
+    if (!p) return STRIX_ERROR_INVALID_ARGUMENT;
+    strix_status s = context_check(p->owner);
+    if (s == STRIX_SUCCESS) s = enqueue_gate_up(p);
+    if (s == STRIX_SUCCESS) s = enqueue_down(p, false);
+    return s;
+}
+strix_status strix_b200_moe_plan_rows(strix_tp_moe_plan p, const float** each, const int32_t** row_valid) {
+    if (each) *each = nullptr;
+    if (row_valid) *row_valid = nullptr;
+    if (!p || !each || !row_valid) return STRIX_ERROR_INVALID_ARGUMENT;
+    *each = p->each;
+    *row_valid = p->device_routed ? p->row_valid : nullptr;
+    return STRIX_SUCCESS;
+}
+
 // Staged diagnostics of the reference's split3 schedule have no counterpart in this one.
 strix_status strix_tp_moe_plan_down_core(strix_tp_moe_plan) { return STRIX_ERROR_NOT_IMPLEMENTED; }
 strix_status strix_tp_moe_plan_down_finish(strix_tp_moe_plan) { return STRIX_ERROR_NOT_IMPLEMENTED; }

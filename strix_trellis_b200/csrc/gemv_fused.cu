@@ -11,22 +11,26 @@
 // c owns the contiguous unit range [c*U/G, (c+1)*U/G): every SM streams the same number
 // of bytes (+-1 unit) through a shared-memory ring filled by 1-D bulk copies.  Sixteen
 // decode warps: warp (t, g) owns column tile t of the units of parity g, so the two warp
-// groups leapfrog through the ring.  A decoded tile is the A operand of mma.sync.m16n8k16 (m = output column), the
-// activation rows are the B operand (n = row), so 1..8 rows cost the same tensor work.
+// groups leapfrog through the ring.  A decoded tile is the A operand of mma.sync.m16n8k16
+// (m = output column), the activation rows are the B operand (n = row), so 1..8 rows cost
+// the same tensor work.
 //
 // Fold: a column block that lies inside one CTA's range is finished by that CTA.  A
 // column block shared by several CTAs is finished by the CTA that holds its FIRST K range
 // -- the end of that CTA's own unit range, so it gets there when everybody else is done or
-// about to be.  The others publish one partial plane each in global scratch, word by word,
-// where a word is either the "empty" pattern (all ones, a NaN no sum produces) or a value:
-// no flag, no fence, no atomic.  The finishing CTA polls the words (bounded), adds the
-// planes in ascending K order from +0 with its own contribution first (never in arrival
-// order; the reference's order, src/gemv_fused.hip:81-127), marks them empty again and
-// applies the output stages.  Waits only point to higher CTA indices, all CTAs of the grid
-// are resident (grid <= SM count), and a wait that runs out reports kTimeoutFold.  All of that is done by
-// a separate epilogue warp: decode warps only drop their accumulators into a double-buffered
-// shared-memory area and move on, so no decode warp ever waits on global-memory latency.
-#include <cstdlib>
+// about to be.  The others publish partial planes in global scratch, word by word, where a
+// word is either the "empty" pattern (all ones, a NaN no sum produces) or a value: no flag,
+// no fence, no atomic.  The finishing CTA polls the words (bounded), adds the planes in
+// ascending K order from +0 with its own contribution first (never in arrival order; the
+// reference's order, src/gemv_fused.hip:81-127), marks them empty again and applies the
+// output stages.  Waits only point to higher CTA indices, all CTAs of the grid are resident
+// (grid <= SM count), and a wait that runs out reports kTimeoutFold.
+//
+// Two kernels share this design.  gemv_fused_kernel serves 2..8 rows (and one row of a
+// layer too wide to stage at once): a separate epilogue warp turns dumped accumulators into
+// planes or outputs.  gemv_row_kernel is the one-row decode case, where the head and the
+// tail of the launch weigh as much as the loop: contributors publish their planes straight from
+// the accumulator registers, and the finishing CTA polls one plane per decode warp.
 #include <type_traits>
 
 #include "backend.h"
@@ -45,24 +49,14 @@ constexpr int kDumpThreads = (kConsumers + 1) * 32;  // decode warps + epilogue 
 constexpr uint32_t kEmptyWord = 0xFFFFFFFFu;      // a partial-plane word nobody has written yet
 constexpr int kActBytes = 64 * 1024;             // staged core input per CTA
 constexpr size_t kGemvSmemLimit = 200 * 1024;    // dynamic shared memory a launch may ask for
-#ifndef ST_GEMV_OCCUPANCY
-#define ST_GEMV_OCCUPANCY 1
-#endif
-#ifndef ST_GEMV_ILP
-#define ST_GEMV_ILP 2
-#endif
-constexpr int kCtasPerSm = ST_GEMV_OCCUPANCY;    // measured: a second resident CTA (the next launch) gains nothing
-constexpr int kTilesInFlight = ST_GEMV_ILP;      // independent tile decodes per warp
+constexpr int kTilesInFlight = 2;                // independent tile decodes per warp
 
 struct GemvArgs {
     LinearCall call;
     Split split;               // unit range of every CTA (units / grid, units % grid)
     int stages;
     int act_blocks;            // H128 blocks of core input staged at a time
-    float* partials;           // [grid][rows][128], every word empty on entry and on exit
-#ifdef ST_TIMELINE
-    unsigned long long* timeline;
-#endif
+    float* partials;           // [grid][rows][128] ([grid][2][128] for the one-row kernel), every word empty on entry and on exit
 };
 
 __host__ __device__ inline int stage_bytes(int bits) { return 2048 * bits; }
@@ -125,11 +119,9 @@ __device__ __forceinline__ void fold_row(const GemvArgs& args, const float* own,
     }
 }
 
-// MULTI selects the code for more than one activation row (several staging items per warp in
-// flight, fold sums in shared memory); the one-row instantiation carries none of it, which
-// keeps the latency-critical head and tail of the decode case as short as they can be.
-template <int K, int CB, bool MULTI>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const GemvArgs args) {
+// Rows 2..8 (and one row of a layer whose core input does not fit the staging area at once).
+template <int K, int CB>
+__global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs args) {
     extern __shared__ __align__(128) unsigned char smem[];
     const LinearCall& c = args.call;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -154,20 +146,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
         mbar_fence_init();
     }
     __syncthreads();
-#ifdef ST_TIMELINE
-    auto stamp = [&](int slot) {
-        if (args.timeline && ((threadIdx.x == 0 && slot != 1 && slot != 5) || (slot == 6 && threadIdx.x == 32 * kConsumers) ||
-                              ((slot == 1 || slot == 5) && threadIdx.x == 32 * (kConsumers + 1)))) {
-            unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-            args.timeline[(size_t)blockIdx.x * 8 + slot] = t;
-            if (slot == 3) args.timeline[(size_t)blockIdx.x * 8 + 7] = (unsigned long long)clock64();
-            if (slot == 4) args.timeline[(size_t)blockIdx.x * 8 + 7] = (unsigned long long)clock64() - args.timeline[(size_t)blockIdx.x * 8 + 7];
-        }
-    };
-#else
-    auto stamp = [](int) {};
-#endif
-    stamp(0);
     pdl_launch_dependents();
 
     if (warp == kConsumers) {
@@ -186,7 +164,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
                 issued = i + 1;
                 if (++st == stages) { st = 0; prev_use ^= 1; }
             }
-            stamp(6);
             // Never leave the CTA with a copy still landing in its shared memory.
             for (int i = (issued > stages ? issued - stages : 0); i < issued; ++i)
                 mbar_wait(full0 + 8 * (i % stages), (i / stages) & 1, c.status, kTimeoutDrain);
@@ -243,13 +220,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
                 // real sum never has the empty pattern (an all-ones NaN), so no flag and no fence
                 for (int e = lane; e < rows * 128; e += 32)
                     st_relaxed_gpu(plane + e, __float_as_uint(__fadd_rn(f0[e], f0[1024 + e])));
-                stamp(1);
             } else {
                 // The block is finished here: it lies inside this CTA's range, or this CTA holds
                 // its FIRST K range -- the end of its own unit range, so every other contributor
                 // finishes at about the same time or earlier.  With several rows and planes to
                 // wait for, the decode warps (idle by then) fold one row each instead.
-                if (!(MULTI && !whole)) {
+                if (whole) {
                     for (int r = 0; r < rows; ++r) fold_row(args, f0, r, rows, nb, first, last, lane, sv, bs);
                 }
             }
@@ -257,7 +233,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
             asm volatile("bar.arrive %0, %1;" ::"r"(4 + buf), "r"(kDumpThreads) : "memory");
             ++flush;
         }
-        stamp(5);
         return;
     }
 
@@ -266,7 +241,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     // CTA's range touches is staged exactly once, at its own slot, before the loop starts.
     // The input scales of a warp's first block are weights (immutable): they are fetched
     // before the wait on the prior grid, so only the activation load follows it.
-    const bool resident = MULTI ? hblocks <= args.act_blocks : true;  // the one-row kernel is only launched resident
+    const bool resident = hblocks <= args.act_blocks;
     const int need = my_units < hblocks ? my_units : hblocks;
     const int hb_first = walk_hb0;
     uint16_t su_first[4] = {0, 0, 0, 0};
@@ -277,7 +252,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
         for (int j = 0; j < 4; ++j) su_first[j] = c.w.suh[(size_t)hb * 128 + lane + 32 * j];
     }
     pdl_wait_prior_grid();  // x may belong to the prior grid
-    stamp(2);
     const int ctile = warp & 7, kgroup = warp >> 3;
     const LaneGeom<K> geom(lane);
     // Row fed by this lane as the B operand.  Rows >= `rows` only reach accumulator
@@ -337,7 +311,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
             if (hb >= hblocks) hb -= hblocks;
             slot = hb;
         };
-        stage_items(rows * need, true, where, std::integral_constant<int, MULTI ? 4 : 1>{});
+        stage_items(rows * need, true, where, std::integral_constant<int, 4>{});
         named_barrier(1, kConsumers * 32);
     }
 
@@ -358,10 +332,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
                 r = item / len;
                 slot = item % len;
                 hb = hb0 + slot;
-            }, std::integral_constant<int, MULTI ? 4 : 1>{});
+            }, std::integral_constant<int, 4>{});
             named_barrier(1, kConsumers * 32);
         }
-        if (done == 0) stamp(3);
 
         // this warp group takes the units of its parity (ring slots alternate with them)
         for (; next < done + len && ok; next += 2) {
@@ -389,7 +362,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
             if (lane == 0) mbar_arrive(empty0 + 8 * st);
         }
         done += len;
-        if (done == my_units) stamp(4);
         if (!((hb0 + len == hblocks) || (done == my_units))) continue;
 
         // ---- drop this CTA's contribution to column block nb and move on --------------------
@@ -415,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     // rest), warp r folds row r -- eight rows wait for their planes side by side instead of one
     // after the other in the epilogue warp.  Every decode warp reaches the barrier, whatever
     // its own waits returned, so it cannot be left short of arrivals.
-    if (MULTI && my_units > 0) {
+    if (my_units > 0) {
         const int blk_lo = final_nb * hblocks, blk_hi = blk_lo + hblocks;
         if (!(mine.begin <= blk_lo && mine.end >= blk_hi)) {
             int first, last;
@@ -437,6 +409,344 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_fused_kernel(const 
     }
 }
 
+
+// ---- one activation row -----------------------------------------------------------------
+namespace {
+constexpr int kRowHeader = 2048 + 8192 + 128 + 512;  // fold buffers, gathered planes, flag, barriers
+static_assert(kRowHeader % 128 == 0, "the ring starts on a 128-byte boundary");
+
+__device__ __forceinline__ uint4 ld_relaxed_gpu_v4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_gpu_v4(uint4* p, uint4 v) {
+    asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ bool any_empty(const uint4& a, const uint4& b) {
+    return a.x == kEmptyWord || a.y == kEmptyWord || a.z == kEmptyWord || a.w == kEmptyWord ||
+           b.x == kEmptyWord || b.y == kEmptyWord || b.z == kEmptyWord || b.w == kEmptyWord;
+}
+
+// One warp waits for one contributor's plane: lane l owns columns 4l..4l+3 of both k-group
+// halves.  The first load is looked at as soon as it is back: measured on the benchmark shapes,
+// most planes are already there when the finishing CTA gets here, and anything that delays the
+// first look (pacing the loads, staggering them) costs more than it gains.  Returns the two
+// halves (every word a value) and marks the plane empty again; false when the bounded wait
+// runs out.
+__device__ __forceinline__ bool await_plane(uint4* g0, uint4* g1, int lane, uint4& a, uint4& b) {
+    bool have = false;
+    for (uint32_t tries = 0; tries < (1u << 20) && !have; ++tries) {
+        a = ld_relaxed_gpu_v4(g0 + lane);
+        b = ld_relaxed_gpu_v4(g1 + lane);
+        have = __all_sync(0xFFFFFFFFu, !any_empty(a, b));
+    }
+    if (have) {
+        const uint4 empty = make_uint4(kEmptyWord, kEmptyWord, kEmptyWord, kEmptyWord);
+        st_relaxed_gpu_v4(g0 + lane, empty);  // empty again for the next launch
+        st_relaxed_gpu_v4(g1 + lane, empty);
+    }
+    return have;
+}
+}  // namespace
+
+// One row, core input resident in shared memory.  Roles: 16 decode warps, one producer warp
+// (bulk copies of the weight stream), one epilogue warp (finishes column blocks that lie
+// wholly inside this CTA's range while the decode warps go on).
+//
+// Head: the producer streams weights from the moment the CTA starts (weights are immutable, so
+// this does not wait for the previous kernel of the stream); the input scales of a warp's
+// H128 block are fetched before the wait on the previous kernel too, so that only the load of
+// the activation row and the input stages follow it, then one barrier, then the first mma.
+// (Decoding a warp's first tiles into registers while that load is in flight was measured:
+// 0.25 us per launch slower, the extra live registers cost more than the overlap gains.)
+//
+// Tail: a CTA whose range BEGINS inside a column block is a contributor to it: its decode
+// warps store their accumulators straight into the CTA's plane in global scratch
+// ([cta][k-group][128] floats), no shared-memory hop and no other warp involved.  The CTA whose
+// range ENDS inside a block (it holds the block's first K range) finishes it: decode warp p
+// waits for plane p (await_plane), the planes meet in shared memory, and warp 0 adds them in
+// ascending K order from +0, its own contribution first, then H128, svh, bias, alpha, beta.
+template <int K, int CB>
+__global__ void __launch_bounds__(kThreads, 1) gemv_row_kernel(const GemvArgs args) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const LinearCall& c = args.call;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hblocks = c.w.inputs / 128;
+    const int cta = (int)blockIdx.x;
+    const Range mine = cta_range(args.split, cta);
+    const int my_units = mine.end - mine.begin;
+    const int stages = args.stages;
+    constexpr int kStage = 2048 * K;
+
+    // shared memory: [2 x fold 1 KB][16 gathered planes 8 KB][flag][barriers 512 B][ring][core input]
+    float* fold_base = reinterpret_cast<float*>(smem);            // [2 buffers][2 k-groups][128]
+    float* gathered = reinterpret_cast<float*>(smem + 2048);      // [16][128]
+    int* gave_up = reinterpret_cast<int*>(smem + 2048 + 8192);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2048 + 8192 + 128);
+    unsigned char* ring = smem + kRowHeader;
+    uint2* act = reinterpret_cast<uint2*>(ring + (size_t)stages * kStage);
+
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + stages);
+    if ((int)threadIdx.x < stages) {  // one thread per ring slot
+        mbar_init(full0 + 8 * threadIdx.x, 1);
+        mbar_init(empty0 + 8 * threadIdx.x, 8);
+        mbar_fence_init();
+    }
+    if (threadIdx.x == 0) *gave_up = 0;
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == kConsumers) {
+        // ---- producer: weights are immutable, so this needs no wait on the prior grid ----
+        if (lane == 0) {
+            const unsigned char* stream =
+                reinterpret_cast<const unsigned char*>(c.w.packed) + (size_t)mine.begin * kStage;
+            int issued = 0;
+            int st = 0;             // ring slot of unit i and the parity of its previous use,
+            uint32_t prev_use = 1;  // stepped without divisions
+            for (int i = 0; i < my_units; ++i) {
+                if (i >= stages && !mbar_wait(empty0 + 8 * st, prev_use, c.status, kTimeoutRingEmpty)) break;
+                mbar_expect_tx(full0 + 8 * st, kStage);
+                bulk_load(smem_u32(ring + (size_t)st * kStage), stream + (size_t)i * kStage, kStage, full0 + 8 * st);
+                issued = i + 1;
+                if (++st == stages) { st = 0; prev_use ^= 1; }
+            }
+            // Never leave the CTA with a copy still landing in its shared memory.
+            for (int i = (issued > stages ? issued - stages : 0); i < issued; ++i)
+                mbar_wait(full0 + 8 * (i % stages), (i / stages) & 1, c.status, kTimeoutDrain);
+        }
+        return;
+    }
+
+    // Walk of the CTA's unit range, cut at column-block ends; shared by decode and epilogue
+    // warps (each calls it once per segment, in order).
+    int walk_nb = mine.begin / hblocks, walk_hb0 = mine.begin - walk_nb * hblocks;
+    auto segment = [&](int done, int& nb, int& hb0, int& len) {
+        nb = walk_nb;
+        hb0 = walk_hb0;
+        len = my_units - done;
+        if (len > hblocks - hb0) len = hblocks - hb0;
+        walk_hb0 += len;
+        if (walk_hb0 == hblocks) { walk_hb0 = 0; ++walk_nb; }
+    };
+    // A segment [hb0, hb0+len) of block nb ends the block or the range.  It is `whole` when the
+    // block lies inside this CTA's range.
+    auto is_whole = [&](int nb) { return mine.begin <= nb * hblocks && mine.end >= (nb + 1) * hblocks; };
+
+    if (warp == kConsumers + 1) {
+        // ---- epilogue warp: output stages of the blocks that need nobody else ---------------
+        pdl_wait_prior_grid();  // y may belong to the prior grid
+        int done = 0, flush = 0;
+        while (done < my_units) {
+            int nb, hb0, len;
+            segment(done, nb, hb0, len);
+            done += len;
+            if (!is_whole(nb)) continue;
+            const int buf = flush & 1;
+            float sv[4], bs[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int cidx = nb * 128 + lane + 32 * j;
+                sv[j] = half_bits_to_float(c.w.svh[cidx]);
+                bs[j] = c.w.bias ? c.w.bias[cidx] : 0.0f;
+            }
+            named_barrier(2 + buf, kDumpThreads);  // all decode warps have dumped into `buf`
+            const float* f0 = fold_base + buf * 256;
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = __fadd_rn(0.f, __fadd_rn(f0[lane + 32 * j], f0[128 + lane + 32 * j]));
+            hadamard128_warp(v, lane);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float* out = c.y + nb * 128 + lane + 32 * j;
+                float value = __fmul_rn(v[j], sv[j]);
+                if (c.w.bias) value = __fadd_rn(value, bs[j]);
+                value = __fmul_rn(value, c.alpha);
+                if (c.beta != 0.0f) value = __fadd_rn(value, __fmul_rn(c.beta, *out));
+                *out = value;
+            }
+            asm volatile("bar.arrive %0, %1;" ::"r"(4 + buf), "r"(kDumpThreads) : "memory");
+            ++flush;
+        }
+        return;
+    }
+
+    // ---- decode warps -------------------------------------------------------------------
+    const int ctile = warp & 7, kgroup = warp >> 3;
+    const LaneGeom<K> geom(lane);
+    const int need = my_units < hblocks ? my_units : hblocks;  // H128 blocks of the row this CTA touches
+    const int hb_first = walk_hb0;
+    int my_hb = hb_first + warp;                               // the block this warp stages (warp < need)
+    if (my_hb >= hblocks) my_hb -= hblocks;
+    uint16_t su[4] = {0, 0, 0, 0};
+    if (warp < need) {  // input scales are weights: fetched before the wait on the prior grid
+#pragma unroll
+        for (int j = 0; j < 4; ++j) su[j] = c.w.suh[(size_t)my_hb * 128 + lane + 32 * j];
+    }
+    pdl_wait_prior_grid();  // x, y and the scratch may belong to the prior grid
+    float xv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (warp < need) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xv[j] = c.x[(size_t)my_hb * 128 + lane + 32 * j];
+    }
+
+    bool ok = true;
+    int slot = kgroup % stages;  // ring slot and use parity of the unit this warp decodes next
+    uint32_t use = (uint32_t)(kgroup / stages) & 1;
+
+    // input stages of this warp's block, written in B-fragment order:
+    // act[(hb*8 + kt)*4 + q] = {half2(k0,k0+1), half2(k0+8,k0+9)}, k0 = 2q
+    __half* act_h = reinterpret_cast<__half*>(act);
+    for (int item = warp; item < need; item += kConsumers) {
+        int hb = hb_first + item;
+        if (hb >= hblocks) hb -= hblocks;
+        float v[4];
+        if (item == warp) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = __half2float(scale_input(xv[j], su[j]));
+        } else {  // more blocks than warps: the rest comes straight from memory
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                v[j] = __half2float(scale_input(c.x[(size_t)hb * 128 + lane + 32 * j], c.w.suh[(size_t)hb * 128 + lane + 32 * j]));
+        }
+        hadamard128_warp(v, lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = lane + 32 * j, kt = e >> 4, kk = e & 15;
+            const int q = (kk & 7) >> 1, hi = kk >> 3, lo = kk & 1;
+            act_h[(((size_t)hb * 8 + kt) * 4 + q) * 4 + hi * 2 + lo] = __float2half_rn(v[j]);
+        }
+    }
+    named_barrier(1, kConsumers * 32);
+
+    // Only activation row 0 exists: lanes of every row feed it as the B operand; accumulator
+    // columns of rows >= 1 are never read.
+    const uint2* act_lane = act + (lane & 3);
+    const int col = ctile * 16 + (lane >> 2);
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    int done = 0, flush = 0;
+    int next = kgroup;  // the unit (relative to the range) this warp decodes next
+    while (done < my_units) {
+        int nb, hb0, len;
+        segment(done, nb, hb0, len);
+        for (; next < done + len && ok; next += 2) {
+            const int b = next - done, st = slot;
+            ok = mbar_wait(full0 + 8 * st, use, c.status, kTimeoutRingFull);
+            if (!ok) break;
+            slot += 2;
+            while (slot >= stages) { slot -= stages; use ^= 1; }
+            const uint32_t* tiles = reinterpret_cast<const uint32_t*>(ring + (size_t)st * kStage) + ctile * (8 * K);
+            const uint2* bsrc = act_lane + (size_t)(hb0 + b) * 32;
+#pragma unroll
+            for (int kt = 0; kt < 8; kt += kTilesInFlight) {
+                uint32_t f[kTilesInFlight][4];
+                uint2 bf[kTilesInFlight];
+#pragma unroll
+                for (int q = 0; q < kTilesInFlight; ++q) {
+                    decode_tile_frag<K, CB>(tiles + (kt + q) * 8 * (8 * K), geom, f[q]);
+                    bf[q] = bsrc[(kt + q) * 4];
+                }
+#pragma unroll
+                for (int q = 0; q < kTilesInFlight; ++q) mma_16816(acc[q & 1], f[q], bf[q].x, bf[q].y);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * st);
+        }
+        done += len;
+
+        // ---- this CTA's contribution to column block nb is complete -------------------------
+        // row 0 of the accumulators: lanes with lane % 4 == 0 hold columns col (c0) and col+8 (c2)
+        const float v_lo = acc[0][0] + acc[1][0], v_hi = acc[0][2] + acc[1][2];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[0][j] = acc[1][j] = 0.f;
+        const int blk_lo = nb * hblocks, blk_hi = blk_lo + hblocks;
+        const bool whole = mine.begin <= blk_lo && mine.end >= blk_hi;
+        if (!whole && mine.begin > blk_lo) {
+            // contributor: publish straight from the registers, k-group planes apart
+            if ((lane & 3) == 0) {
+                uint32_t* plane = reinterpret_cast<uint32_t*>(args.partials) + ((size_t)cta * 2 + kgroup) * 128;
+                st_relaxed_gpu(plane + col, __float_as_uint(v_lo));
+                st_relaxed_gpu(plane + col + 8, __float_as_uint(v_hi));
+            }
+            continue;
+        }
+        const int buf = flush & 1;
+        if (flush >= 2) named_barrier(4 + buf, kDumpThreads);  // the epilogue warp is done with `buf`
+        if ((lane & 3) == 0) {
+            float* g = fold_base + buf * 256 + kgroup * 128;
+            g[col] = v_lo;
+            g[col + 8] = v_hi;
+        }
+        ++flush;
+        if (whole) {
+            asm volatile("bar.arrive %0, %1;" ::"r"(2 + buf), "r"(kDumpThreads) : "memory");
+            continue;
+        }
+
+        // ---- this CTA holds the block's first K range: it finishes the block ----------------
+        // (the block goes on in later CTAs, so this is the end of the range)
+        int first, last;
+        contributors(args.split, blk_lo, blk_hi, first, last);
+        const int planes = last - cta;
+        float sv[4], bs[4], v[4];
+        if (warp == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int cidx = nb * 128 + lane + 32 * j;
+                sv[j] = half_bits_to_float(c.w.svh[cidx]);
+                bs[j] = c.w.bias ? c.w.bias[cidx] : 0.0f;
+            }
+        }
+        for (int base = 0; base < planes; base += kConsumers) {
+            const int p = base + warp;
+            if (p < planes) {
+                uint4* g0 = reinterpret_cast<uint4*>(args.partials + ((size_t)(cta + 1 + p) * 2) * 128);
+                uint4 a, bq;
+                if (await_plane(g0, g0 + 32, lane, a, bq)) {
+                    float4 sum;  // the contributor's own order: k-group 0 + k-group 1
+                    sum.x = __fadd_rn(__uint_as_float(a.x), __uint_as_float(bq.x));
+                    sum.y = __fadd_rn(__uint_as_float(a.y), __uint_as_float(bq.y));
+                    sum.z = __fadd_rn(__uint_as_float(a.z), __uint_as_float(bq.z));
+                    sum.w = __fadd_rn(__uint_as_float(a.w), __uint_as_float(bq.w));
+                    reinterpret_cast<float4*>(gathered + warp * 128)[lane] = sum;
+                } else if (lane == 0) {
+                    atomicOr(c.status, kTimeoutFold);
+                    *gave_up = 1;
+                }
+            }
+            named_barrier(1, kConsumers * 32);  // planes of this round (and, first time, the dumps) are in shared memory
+            if (warp == 0) {
+                if (base == 0) {
+                    const float* f0 = fold_base + buf * 256;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[j] = __fadd_rn(0.f, __fadd_rn(f0[lane + 32 * j], f0[128 + lane + 32 * j]));
+                }
+                const int n = planes - base < kConsumers ? planes - base : kConsumers;
+                for (int q = 0; q < n; ++q) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[j] = __fadd_rn(v[j], gathered[q * 128 + lane + 32 * j]);
+                }
+            }
+            if (base + kConsumers < planes) named_barrier(1, kConsumers * 32);  // before `gathered` is reused
+        }
+        if (warp == 0 && ok && *gave_up == 0) {  // a wait that ran out leaves the block unwritten
+            hadamard128_warp(v, lane);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float* out = c.y + nb * 128 + lane + 32 * j;
+                float value = __fmul_rn(v[j], sv[j]);
+                if (c.w.bias) value = __fadd_rn(value, bs[j]);
+                value = __fmul_rn(value, c.alpha);
+                if (c.beta != 0.0f) value = __fadd_rn(value, __fmul_rn(c.beta, *out));
+                *out = value;
+            }
+        }
+    }
+}
+
 // ---- host side -------------------------------------------------------------------------
 static int gemv_grid(const DeviceWeights& w, int sm_count) {
     const long long units = (long long)(w.inputs / 128) * (w.outputs / 128);
@@ -451,7 +761,10 @@ GemvPlan plan_gemv(const DeviceWeights& w, int rows, int sm_count) {
     const int per_cta = (int)((units + grid - 1) / grid);
     int act_blocks = kActBytes / (256 * rows);
     if (act_blocks > hblocks) act_blocks = hblocks;
-    const int ring_budget = 200 * 1024 - 16384 - 512 - act_blocks * 256 * rows;
+    // the one-row kernel: whole row resident, its own (smaller) header and plane layout
+    const bool row_kernel = rows == 1 && hblocks <= act_blocks;
+    const int header = row_kernel ? kRowHeader : 16384 + 512;
+    const int ring_budget = (int)kGemvSmemLimit - header - act_blocks * 256 * rows;
     int stages = ring_budget / stage_bytes(w.bits);
     const int want = (128 * 1024) / stage_bytes(w.bits);  // enough bytes in flight per SM to cover HBM latency
     if (stages > want) stages = want;
@@ -462,13 +775,14 @@ GemvPlan plan_gemv(const DeviceWeights& w, int rows, int sm_count) {
     plan.act_blocks = act_blocks;
     plan.splits = (grid + nblocks - 1) / nblocks;  // typical K partitions of a column block
     plan.stages = stages;
-    plan.smem_bytes = 16384 + 512 + (size_t)stages * stage_bytes(w.bits) + (size_t)act_blocks * 256 * rows;
+    plan.smem_bytes = header + (size_t)stages * stage_bytes(w.bits) + (size_t)act_blocks * 256 * rows;
     plan.counter_bytes = 0;  // the fold needs no counters
-    plan.partial_bytes = align_up((size_t)grid * rows * 128 * sizeof(float));
+    // one plane per CTA and row; the one-row kernel keeps its two k-group halves apart
+    plan.partial_bytes = align_up((size_t)grid * (row_kernel ? 2 : rows) * 128 * sizeof(float));
     return plan;
 }
 
-template <int K, int CB, bool MULTI>
+template <int K, int CB, bool ROW>
 static cudaError_t launch_rows(const GemvArgs& args, int grid, size_t smem, bool pdl, cudaStream_t stream) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
@@ -480,14 +794,15 @@ static cudaError_t launch_rows(const GemvArgs& args, int grid, size_t smem, bool
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_fused_kernel<K, CB, MULTI>, args);
+    if (ROW) return cudaLaunchKernelEx(&cfg, gemv_row_kernel<K, CB>, args);
+    return cudaLaunchKernelEx(&cfg, gemv_fused_kernel<K, CB>, args);
 }
 
 template <int K, int CB>
 static cudaError_t launch_one(const GemvArgs& args, int grid, size_t smem, bool pdl, cudaStream_t stream) {
-    const bool lean = args.call.rows == 1 && args.call.w.inputs / 128 <= args.act_blocks;
-    return lean ? launch_rows<K, CB, false>(args, grid, smem, pdl, stream)
-                : launch_rows<K, CB, true>(args, grid, smem, pdl, stream);
+    const bool row_kernel = args.call.rows == 1 && args.call.w.inputs / 128 <= args.act_blocks;
+    return row_kernel ? launch_rows<K, CB, true>(args, grid, smem, pdl, stream)
+                      : launch_rows<K, CB, false>(args, grid, smem, pdl, stream);
 }
 
 template <int CB>
@@ -509,10 +824,10 @@ static cudaError_t launch_bits(const GemvArgs& a, int g, size_t smem, bool pdl, 
 // when a context is created on a device (configure_device), never on the launch path.
 template <int K, int CB>
 static cudaError_t configure_rate() {
-    cudaError_t e = cudaFuncSetAttribute(gemv_fused_kernel<K, CB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemv_row_kernel<K, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kGemvSmemLimit);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemv_fused_kernel<K, CB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(gemv_fused_kernel<K, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kGemvSmemLimit);
     return e;
 }
@@ -552,9 +867,6 @@ cudaError_t launch_gemv(const LinearCall& call, const GemvPlan& plan, void* work
     args.stages = plan.stages;
     args.act_blocks = plan.act_blocks;
     args.partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + plan.counter_bytes);
-#ifdef ST_TIMELINE
-    if (const char* t = getenv("STRIX_TL")) args.timeline = (unsigned long long*)strtoull(t, nullptr, 16);
-#endif
     switch (call.w.codebook) {
     case CB_3INST: return launch_bits<CB_3INST>(args, plan.grid, plan.smem_bytes, programmatic_launch, stream);
     case CB_MCG: return launch_bits<CB_MCG>(args, plan.grid, plan.smem_bytes, programmatic_launch, stream);

@@ -286,8 +286,8 @@ cudaError_t launch_swiglu(const float* gate, const float* up, float* hidden, int
 __global__ void __launch_bounds__(1024) moe_route_kernel(const unsigned int* __restrict__ ids,
                                                          const float* __restrict__ scores, int tokens, int top_k,
                                                          const MoeBankEntry* __restrict__ bank, int bank_count,
-                                                         GroupedProblem* gate_up, GroupedProblem* down,
-                                                         int* row_valid) {
+                                                         const MoeWindow window, GroupedProblem* gate_up,
+                                                         GroupedProblem* down, int* row_valid) {
     __shared__ int count[1024], first_problem[1024], cursor[1024], scan[1024];
     const int tid = threadIdx.x, routes = tokens * top_k;
     count[tid] = 0;
@@ -298,13 +298,16 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const unsigned int* __r
         for (int s = 0; s < top_k && valid; ++s) {
             const unsigned int id = ids[t * top_k + s];
             const float sc = scores[t * top_k + s];
-            if (id >= (unsigned int)bank_count || !(sc >= 0.0f && sc <= 3.402823466e+38f)) valid = false;
+            if (id >= (unsigned int)window.experts_total || !(sc >= 0.0f && sc <= 3.402823466e+38f)) valid = false;
             for (int q = 0; q < s && valid; ++q)
                 if (ids[t * top_k + q] == id) valid = false;
         }
         row_valid[t] = valid ? 1 : 0;
         if (valid)
-            for (int s = 0; s < top_k; ++s) atomicAdd(&count[ids[t * top_k + s]], 1);
+            for (int s = 0; s < top_k; ++s) {  // routes to experts of another rank run nothing here
+                const unsigned int e = ids[t * top_k + s] - (unsigned int)window.first_expert;
+                if (e < (unsigned int)bank_count) atomicAdd(&count[e], 1);
+            }
     }
     __syncthreads();
     const int n = tid < bank_count ? count[tid] : 0;
@@ -333,7 +336,9 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const unsigned int* __r
     for (int r = tid; r < routes; r += 1024) {
         const int t = r / top_k;
         if (!row_valid[t]) continue;
-        const int e = (int)ids[r];
+        const unsigned int local = ids[r] - (unsigned int)window.first_expert;
+        if (local >= (unsigned int)bank_count) continue;
+        const int e = (int)local;
         const int pos = atomicAdd(&cursor[e], 1);
         const int q = first_problem[e] + pos / kGroupRows, j = pos % kGroupRows;
         gate_up[2 * q].x_row[j] = gate_up[2 * q + 1].x_row[j] = t;
@@ -343,17 +348,19 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const unsigned int* __r
 }
 
 cudaError_t launch_moe_route(const unsigned int* route_ids, const float* route_scores, int tokens, int top_k,
-                             const MoeBankEntry* bank, int bank_count, GroupedProblem* gate_up, GroupedProblem* down,
-                             int* row_valid, cudaStream_t stream) {
-    if (bank_count > 1024) return cudaErrorInvalidValue;
-    moe_route_kernel<<<1, 1024, 0, stream>>>(route_ids, route_scores, tokens, top_k, bank, bank_count, gate_up, down,
-                                             row_valid);
+                             const MoeBankEntry* bank, int bank_count, MoeWindow window, GroupedProblem* gate_up,
+                             GroupedProblem* down, int* row_valid, cudaStream_t stream) {
+    if (bank_count > 1024 || window.first_expert < 0 || window.experts_total < window.first_expert + bank_count)
+        return cudaErrorInvalidValue;
+    moe_route_kernel<<<1, 1024, 0, stream>>>(route_ids, route_scores, tokens, top_k, bank, bank_count, window, gate_up,
+                                             down, row_valid);
     return cudaGetLastError();
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ each, const float* __restrict__ scores,
                                    const int* __restrict__ row_valid, int tokens, int top_k, int outputs,
-                                   float* y, long long y_stride, float alpha, float beta) {
+                                   float* y, long long y_stride, float alpha, float beta,
+                                   const unsigned int* __restrict__ route_ids, int first_expert, int bank_count) {
     const long long total = (long long)tokens * outputs;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -367,6 +374,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ each, const float* 
         for (int s = 0; s < top_k; ++s) {  // ascending slot order from +0
             const float score = scores[t * top_k + s];
             if (score == 0.0f) continue;
+            if (route_ids && route_ids[t * top_k + s] - (unsigned int)first_expert >= (unsigned int)bank_count) continue;
             sum = __fadd_rn(sum, __fmul_rn(score, each[((long long)t * top_k + s) * outputs + n]));
         }
         float value = __fmul_rn(alpha, sum);
@@ -377,12 +385,12 @@ __global__ void moe_combine_kernel(const float* __restrict__ each, const float* 
 
 cudaError_t launch_moe_combine(const float* each, const float* scores, const int* row_valid, int tokens,
                                int top_k, int outputs, float* y, long long y_stride, float alpha, float beta,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, const unsigned int* route_ids, int first_expert, int bank_count) {
     const long long total = (long long)tokens * outputs;
     if (total <= 0) return cudaSuccess;
     const long long want = (total + 255) / 256;
     moe_combine_kernel<<<(int)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(
-        each, scores, row_valid, tokens, top_k, outputs, y, y_stride, alpha, beta);
+        each, scores, row_valid, tokens, top_k, outputs, y, y_stride, alpha, beta, route_ids, first_expert, bank_count);
     return cudaGetLastError();
 }
 

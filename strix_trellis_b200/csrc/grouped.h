@@ -46,14 +46,22 @@ cudaError_t launch_swiglu(const float* gate, const float* up, float* hidden, int
 // groups the valid routes by expert into problem slots of up to kGroupRows rows each
 // (slot tables hold tokens*top_k slots; unused ones get rows = 0).
 struct MoeBankEntry { DeviceWeights gate, up, down; };
+// The bank is a window of the router's id space: id g is bank entry g - first_expert when that
+// lies in [0, bank_count), belongs to another rank when g < experts_total (its slot runs nothing
+// here and does not invalidate the row), and is invalid otherwise.  first_expert = 0 and
+// experts_total = bank_count is the single-rank case.
+struct MoeWindow { int first_expert, experts_total; };
 cudaError_t launch_moe_route(const unsigned int* route_ids, const float* route_scores, int tokens, int top_k,
-                             const MoeBankEntry* bank, int bank_count, GroupedProblem* gate_up, GroupedProblem* down,
-                             int* row_valid, cudaStream_t stream);
+                             const MoeBankEntry* bank, int bank_count, MoeWindow window, GroupedProblem* gate_up,
+                             GroupedProblem* down, int* row_valid, cudaStream_t stream);
 
 // Routed-expert combine: y[t] = alpha * sum_{s ascending, from +0} RN32(score[t,s]*each[t,s]) + beta*y[t];
 // a zero score skips its slot; a row flagged invalid becomes NaN (src/tp_moe.hip:112-164).
+// With `route_ids` and a window, slots whose expert lives on another rank are skipped: the
+// result is this rank's contribution (the reference's per-rank semantics, include/strix_trellis.h:215-216).
 cudaError_t launch_moe_combine(const float* each, const float* scores, const int* row_valid, int tokens,
                                int top_k, int outputs, float* y, long long y_stride, float alpha, float beta,
-                               cudaStream_t stream);
+                               cudaStream_t stream, const unsigned int* route_ids = nullptr, int first_expert = 0,
+                               int bank_count = 0);
 
 }  // namespace st

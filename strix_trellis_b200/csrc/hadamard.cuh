@@ -12,14 +12,17 @@ namespace st {
 // One warp transforms one 128-block.  Lane l holds elements l, l+32, l+64, l+96.
 // Strides 1..16 cross lanes (butterfly partner = lane ^ stride), strides 32 and 64
 // stay in registers; order and operand sides match the ascending-stride reference:
-// lower index gets lo+hi, upper index gets lo-hi.
+// lower index gets lo+hi, upper index gets lo-hi.  Across lanes both cases are ONE fused
+// multiply-add, peer + sign*v with sign = +1 (lower) or -1 (upper): the product is exact, so
+// the single rounding is that of the add or subtract.
 __device__ __forceinline__ void hadamard128_warp(float (&v)[4], int lane) {
 #pragma unroll
     for (int stride = 1; stride < 32; stride <<= 1) {
+        const float sign = (lane & stride) ? -1.0f : 1.0f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float peer = __shfl_xor_sync(0xFFFFFFFFu, v[j], stride);
-            v[j] = (lane & stride) ? __fsub_rn(peer, v[j]) : __fadd_rn(v[j], peer);
+            v[j] = __fmaf_rn(v[j], sign, peer);
         }
     }
     {   // stride 32: pairs (0,1) and (2,3)

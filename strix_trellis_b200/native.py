@@ -132,6 +132,27 @@ class GroupedGemvDesc(C.Structure):
 P = C.POINTER
 # name -> (restype, argtypes).  Every symbol declared in include/*.h is listed here;
 # tests check that the library exports each of them.
+PEER_RANKS, PEER_HANDLE_BYTES, PEER_CONTROL_BYTES = 8, 64, 2304
+
+
+class PeerMatrix(C.Structure):
+    _fields_ = [("block", vp * PEER_RANKS), ("result", vp * PEER_RANKS), ("width", u32 * PEER_RANKS),
+                ("col_at", u32 * PEER_RANKS), ("total_cols", u64), ("region", u64)]
+
+
+class PeerGatherDesc(C.Structure):
+    _fields_ = [("struct_size", u32), ("abi_version", u32), ("matrices", u32), ("flags", u32),
+                ("rows", u32 * PEER_RANKS), ("row_at", u32 * PEER_RANKS), ("matrix", PeerMatrix * 3),
+                ("reserved", u64 * 2)]
+
+
+class PeerReturnDesc(C.Structure):
+    _fields_ = [("struct_size", u32), ("abi_version", u32), ("each", vp * PEER_RANKS), ("ids", vp * PEER_RANKS),
+                ("row_valid", vp * PEER_RANKS), ("first_expert", u32 * PEER_RANKS), ("experts", u32 * PEER_RANKS),
+                ("tokens", u32), ("tokens_per_rank", u32), ("top_k", u32), ("flags", u32), ("width", u64),
+                ("region", u64), ("reserved", u64 * 2)]
+
+
 PROTOTYPES = {
     "strix_get_abi_version": (u32, []),
     "strix_status_string": (C.c_char_p, [C.c_int]),
@@ -199,6 +220,17 @@ PROTOTYPES = {
     "strix_b200_gemv_splits": (C.c_int, [vp, vp, u32, P(u32)]),
     "strix_b200_gemv_partition": (C.c_int, [u64, u64, u32, u32, u64, P(u64)]),
     "strix_b200_moe_combine": (C.c_int, [vp, vp, vp, u32, u32, u32, vp, u64, f32, f32, P(Stream)]),
+    "strix_b200_moe_combine_rows": (C.c_int, [vp, vp, vp, vp, u32, u32, u32, vp, u64, f32, f32, P(Stream)]),
+    "strix_b200_moe_plan_set_window": (C.c_int, [vp, u32, u32]),
+    "strix_b200_moe_plan_projections": (C.c_int, [vp]),
+    "strix_b200_moe_plan_rows": (C.c_int, [vp, P(vp), P(vp)]),
+    "strix_b200_peer_arena_create": (C.c_int, [vp, u64, P(vp), C.c_char_p]),
+    "strix_b200_peer_arena_destroy": (C.c_int, [vp, vp]),
+    "strix_b200_peer_group_create": (C.c_int, [vp, P(vp), u32, u32, u64, C.c_char_p, u32, P(vp)]),
+    "strix_b200_peer_group_destroy": (C.c_int, [vp]),
+    "strix_b200_peer_sum": (C.c_int, [vp, P(vp), u64, u64, P(Stream)]),
+    "strix_b200_peer_gather": (C.c_int, [vp, P(PeerGatherDesc), P(Stream)]),
+    "strix_b200_peer_return_routes": (C.c_int, [vp, P(PeerReturnDesc), P(Stream)]),
     "strix_b200_device_status": (C.c_int, [vp, P(u32)]),
     "strix_b200_set_programmatic_launch": (C.c_int, [vp, u32]),
     "strix_b200_gemv_noalloc": (C.c_int, [vp, P(MatmulDesc), P(Stream)]),

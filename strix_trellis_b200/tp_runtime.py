@@ -1,25 +1,38 @@
 """Tensor- and expert-parallel layers over the per-rank C ABI: every rank runs the complete
-local operator on its shard (one process per GPU) and torch.distributed (NCCL over NVLink)
-runs only at the shard boundary.  Math contract of the reference (docs/TP_RANK.md:150-156):
-row-parallel outputs are summed, column-parallel outputs are concatenated in rank order,
-the bias lives on exactly one rank, expert outputs are combined at the token's home rank in
-ascending slot order.  No kernel reads peer memory.
+local operator on its shard (one process per GPU) and the ranks meet only at the shard
+boundary, through peer memory over NVLink (strix_b200_peer_*, one kernel per exchange, no
+library collective on the forward path).  Math contract of the reference
+(docs/TP_RANK.md:150-156): row-parallel outputs are summed, column-parallel outputs are
+concatenated in rank order, the bias lives on exactly one rank, expert outputs are combined at
+the token's home rank in ascending slot order.
+
+Every forward is a fixed sequence of kernel launches on the caller's current stream: no host
+synchronisation, no allocation after the first call, capturable into a CUDA graph on any number
+of ranks.  A plan is frozen for the stream it was first used on; using a layer from another
+stream builds another plan (plans are cached per stream and buffer set).
 """
 import numpy as np
 import torch
 
 from . import tp
-from .runtime import DensePlan, MoePlan
+from .peer import PeerGroup
+from .runtime import DensePlan, MoePlan, _cur_stream
+from . import native as N
+import ctypes as C
+
+
+def _stream_key():
+    return torch.cuda.current_stream().cuda_stream
 
 
 class RowParallelLinear:
     """Input (split-K) partition: rank r multiplies its slice of x by its K slice of the
-    weights; all-reduce(sum) of the [rows, N] partial outputs."""
+    weights; the [rows, N] partial outputs are summed over the ranks in rank order."""
 
-    def __init__(self, ctx, tensor, rank, world, group=None, bias_rank=0, full_inputs=None):
+    def __init__(self, ctx, tensor, rank, world, group=None, bias_rank=0, full_inputs=None, max_rows=8):
         """`tensor` is the whole layer, or (with `full_inputs` = the layer's input size) this
         rank's shard already cut, e.g. by a loader that reads only its own slice."""
-        self.rank, self.world, self.group = rank, world, group
+        self.rank, self.world = rank, world
         self.bounds = tp.h128_bounds(full_inputs or tensor.input_size, world)
         shard = tensor if full_inputs else tp.rank_partition(tensor, "input", rank, world, bias_rank=bias_rank)
         a0, a1 = self.bounds[rank]
@@ -27,55 +40,83 @@ class RowParallelLinear:
             raise ValueError("shard does not match this rank's input range")
         self.weights = ctx.prepare(shard)
         self.plans = {}
+        self.ctx, self.group, self.peers = ctx, group, None
+        self.max_rows = max_rows
+
+    def _exchange(self):
+        """The exchange arena, set up (collectively: every rank must get here) at the first
+        forward; `local` alone never needs it."""
+        if self.peers is None:
+            payload = self.world * self.max_rows * self.weights.outputs * 4
+            self.peers = PeerGroup(self.ctx, 2 * payload + 4096, self.rank, self.world, self.group)
+            self.region = self.peers.reserve(payload)
+        return self.peers
 
     def local(self, x_full, y=None):
         """y = Linear_r(x_full[:, a0:a1]) on the strided column view, no copy.  Plans are
-        frozen per (activation buffer, output buffer) pair and reused."""
+        frozen per (stream, activation buffer, output buffer) and reused."""
         a0, a1 = self.bounds[self.rank]
         if y is None:
             y = torch.empty((x_full.shape[0], self.weights.outputs), dtype=torch.float32, device=x_full.device)
-        key = (x_full.data_ptr(), tuple(x_full.shape), x_full.stride(0), y.data_ptr(), y.stride(0))
+        key = (_stream_key(), x_full.data_ptr(), tuple(x_full.shape), x_full.stride(0), y.data_ptr(), y.stride(0))
         plan = self.plans.get(key)
         if plan is None:
             plan = self.plans[key] = DensePlan(self.weights, x_full[:, a0:a1], y)
         plan.submit()
         return y
 
+    def forward(self, x_full, y=None):
+        y = self.local(x_full, y)
+        if self.world > 1:
+            if y.shape[0] > self.max_rows or not y.is_contiguous():
+                raise ValueError("row count beyond the exchange region this layer reserved")
+            self._exchange().sum_rows([y], self.region)
+        return y
+
     def close(self):
         for plan in self.plans.values():
             plan.close()
         self.plans.clear()
+        if self.peers:
+            self.peers.close()
         self.weights.close()
-
-    def forward(self, x_full, y=None):
-        y = self.local(x_full, y)
-        if self.world > 1:
-            tp.all_reduce_rows(y, self.group)
-        return y
 
 
 class ColumnParallelLinear:
-    """Output partition (LM head): rank r owns an H128-aligned column range; all-gather of
-    the logits (padded to the widest shard when the block count does not divide)."""
+    """Output partition (LM head): rank r owns an H128-aligned column range; every rank's block
+    of logits is stored into every rank's result at its column offset (uneven shards need no
+    padding)."""
 
-    def __init__(self, ctx, tensor, rank, world, group=None, full_outputs=None):
-        self.rank, self.world, self.group = rank, world, group
+    def __init__(self, ctx, tensor, rank, world, group=None, full_outputs=None, max_rows=8):
+        self.rank, self.world = rank, world
         self.bounds = tp.h128_bounds(full_outputs or tensor.output_size, world)
         self.widths = [b - a for a, b in self.bounds]
+        self.total = self.bounds[-1][1]
         shard = tensor if full_outputs else tp.rank_partition(tensor, "output", rank, world)
         if shard.output_size != self.widths[rank]:
             raise ValueError("shard does not match this rank's output range")
         self.weights = ctx.prepare(shard)
-        self.plans, self.outputs = {}, {}
+        self.plans, self.blocks, self.results = {}, {}, {}
+        self.ctx, self.group, self.peers = ctx, group, None
+        self.max_rows = max_rows
+
+    def _exchange(self):
+        """The exchange arena, set up (collectively: every rank must get here) at the first
+        forward; `local` alone never needs it."""
+        if self.peers is None:
+            payload = self.max_rows * self.total * 4
+            self.peers = PeerGroup(self.ctx, 2 * payload + 4096, self.rank, self.world, self.group)
+            self.region = self.peers.reserve(payload)
+        return self.peers
 
     def local(self, x, y=None):
-        """This rank's logits block; plans are frozen per (activation, output) buffer pair."""
+        """This rank's logits block; plans are frozen per (stream, activation, output) buffers."""
         if y is None:
-            y = self.outputs.get((x.shape[0], x.device))
+            y = self.blocks.get((x.shape[0], x.device))
             if y is None:
-                y = self.outputs[(x.shape[0], x.device)] = torch.empty(
+                y = self.blocks[(x.shape[0], x.device)] = torch.empty(
                     (x.shape[0], self.weights.outputs), dtype=torch.float32, device=x.device)
-        key = (x.data_ptr(), tuple(x.shape), x.stride(0), y.data_ptr(), y.stride(0))
+        key = (_stream_key(), x.data_ptr(), tuple(x.shape), x.stride(0), y.data_ptr(), y.stride(0))
         plan = self.plans.get(key)
         if plan is None:
             plan = self.plans[key] = DensePlan(self.weights, x, y)
@@ -83,106 +124,158 @@ class ColumnParallelLinear:
         return y
 
     def forward(self, x):
+        """[rows, full outputs] logits; the tensor is reused by the next forward of the same row
+        count."""
         y = self.local(x)
-        return y if self.world == 1 else tp.all_gather_columns(y, self.widths, self.group)
+        if self.world == 1:
+            return y
+        rows = x.shape[0]
+        if rows > self.max_rows:
+            raise ValueError("row count beyond the exchange region this layer reserved")
+        out = self.results.get(rows)
+        if out is None:
+            out = self.results[rows] = torch.empty((rows, self.total), dtype=torch.float32, device=x.device)
+        self._exchange().gather([rows] * self.world, [0] * self.world,
+                          [dict(blocks=[y], results=[out], widths=self.widths, col_at=[a for a, _ in self.bounds],
+                                total_cols=self.total, region=self.region)])
+        return out
 
     def close(self):
         for plan in self.plans.values():
             plan.close()
         self.plans.clear()
+        if self.peers:
+            self.peers.close()
         self.weights.close()
 
 
 class ExpertParallelMoE:
-    """Experts owned contiguously (expert e on rank e // ceil(E/world)).  A step:
-    dispatch every (token, slot) row to the owner of its expert (all-to-all), run the
-    owner's experts on the received rows (a device-routed plan with one route per row and
-    score 1, so a row's output IS down_e(SwiGLU(...)) bit for bit), return the rows
-    (all-to-all) and combine at the token's home rank in ascending slot order from +0.
+    """Experts owned contiguously (expert e on rank e // ceil(E/world)); tokens live rank-major
+    (`max_tokens` slots per rank).  A step:
 
-    The exchange uses a fixed capacity per rank pair (max_tokens * top_k rows, unused slots
-    carry an invalid expert id and run nothing), so a step needs no host synchronisation:
-    packing, the three collectives, the expert kernels and the combine are all enqueued."""
+      1. every rank's token rows, route ids and scores are stored into every rank (one
+         exchange): all ranks see all routes and apply the same row rules, so they agree on
+         which rows are valid without talking about it;
+      2. a device-routed plan whose bank is this rank's window of the expert ids runs routing,
+         gate/up, SwiGLU and down for the routes this rank owns (an expert's weights are read
+         once per eight rows routed to it, whoever sent them);
+      3. each owner stores the output row of route (t, s) into the home rank of token t (second
+         exchange);
+      4. the home rank combines its tokens' rows in ascending slot order from +0, a zero score
+         skips its slot, an invalid route row becomes NaN -- bit for bit what the single-rank
+         plan does, which a sum across ranks would not give.
 
-    INVALID = 0x7FFFFFFF
+    Two exchanges per step keep every payload at a fixed address, so the step is five kernels
+    and two exchanges on one stream with nothing on the host in between."""
+
+    PAD = 0xFFFFFFFF  # route id of an empty token slot: invalid on every rank, runs nothing
 
     def __init__(self, ctx, local_experts, experts_total, rank, world, model, max_tokens, top_k, group=None):
-        self.ctx, self.rank, self.world, self.group = ctx, rank, world, group
+        self.ctx, self.rank, self.world = ctx, rank, world
         self.per_rank = -(-experts_total // world)
-        self.model, self.top_k = model, top_k
-        self.cap = max_tokens * top_k  # rows one rank can send to (or receive from) one rank
-        rows = world * self.cap
+        self.first = rank * self.per_rank
+        if len(local_experts) != min(self.per_rank, experts_total - self.first):
+            raise ValueError("this rank owns a different number of experts")
+        self.model, self.top_k, self.slots = model, top_k, max_tokens
+        self.tokens_all = world * max_tokens
         f32 = dict(dtype=torch.float32, device="cuda")
-        self.send_x = torch.zeros((rows, model), **f32)
-        self.recv_x = self.send_x if world == 1 else torch.zeros((rows, model), **f32)
-        self.send_ids = torch.full((rows,), self.INVALID, dtype=torch.int32, device="cuda")
-        self.recv_ids = self.send_ids if world == 1 else torch.full((rows,), self.INVALID, dtype=torch.int32, device="cuda")
-        self.out_rows = torch.zeros((rows, model), **f32)
-        self.back = self.out_rows if world == 1 else torch.zeros((rows, model), **f32)
-        self.ones = torch.ones((rows,), **f32)
-        self.rank_ids = torch.arange(world, device="cuda")
-        self.plan = MoePlan(ctx, local_experts, self.recv_x, self.out_rows, self.recv_ids, self.ones, device_routed=True)
-        self.graphs = []
+        self.x_in = torch.zeros((max_tokens, model), **f32)
+        self.ids_in = torch.full((max_tokens, top_k), self.PAD - (1 << 32), dtype=torch.int32, device="cuda")
+        self.sc_in = torch.zeros((max_tokens, top_k), **f32)
+        self.y = torch.zeros((max_tokens, model), **f32)
+        self.peers = None
+        if world == 1:
+            x_all, ids_all, sc_all = self.x_in, self.ids_in, self.sc_in
+        else:
+            sizes = [self.tokens_all * model * 4, self.tokens_all * top_k * 4, self.tokens_all * top_k * 4,
+                     max_tokens * top_k * model * 4]
+            self.peers = PeerGroup(ctx, 2 * sum(sizes) + 8192, rank, world, group)
+            self.regions = [self.peers.reserve(n) for n in sizes]
+            # the gather is this group's exchange 1, 3, 5, ... (parity 1), the return 2, 4, ... (parity 0)
+            x_all = self.peers.view(0, self.regions[0] + sizes[0], (self.tokens_all, model))
+            ids_all = self.peers.view(0, self.regions[1] + sizes[1], (self.tokens_all, top_k), torch.int32)
+            sc_all = self.peers.view(0, self.regions[2] + sizes[2], (self.tokens_all, top_k))
+            self.back = self.peers.view(0, self.regions[3], (max_tokens, top_k, model))
+        self.ids_all = ids_all
+        self.sink = torch.zeros((self.tokens_all, model), **f32)  # the plan's own (unused) output
+        self.plan = MoePlan(ctx, local_experts, x_all, self.sink, ids_all, sc_all, device_routed=True)
+        N.check(ctx.lib.strix_b200_moe_plan_set_window(self.plan.handle, self.first, experts_total), "set_window")
+        each, valid = N.vp(), N.vp()
+        N.check(ctx.lib.strix_b200_moe_plan_rows(self.plan.handle, C.byref(each), C.byref(valid)), "plan_rows")
+        self.each_ptr, self.valid_ptr = each.value, valid.value
+        self.plan_stream = _stream_key()
+
+    def stage(self, x, route_ids, route_scores):
+        """Copies one step's inputs into the layer's static buffers (device copies on the current
+        stream).  x [T, model] float32; route_ids [T, top_k] global expert ids; T <= max_tokens."""
+        x = torch.as_tensor(x, device="cuda")
+        tokens = x.shape[0]
+        ids = torch.as_tensor(np.asarray(route_ids) if not torch.is_tensor(route_ids) else route_ids, device="cuda")
+        scores = torch.as_tensor(np.asarray(route_scores, dtype=np.float32) if not torch.is_tensor(route_scores)
+                                 else route_scores, device="cuda")
+        if tokens > self.slots or tuple(ids.shape) != (tokens, self.top_k):
+            raise ValueError("routes exceed the capacity this layer was created for")
+        self.x_in[:tokens].copy_(x, non_blocking=True)
+        self.ids_in[:tokens].copy_(ids.to(torch.int64).bitwise_and(0xFFFFFFFF).to(torch.int32) if ids.dtype != torch.int32
+                                   else ids, non_blocking=True)
+        self.ids_in[tokens:].fill_(self.PAD - (1 << 32))
+        self.sc_in[:tokens].copy_(scores.to(torch.float32), non_blocking=True)
+        return tokens
+
+    def run(self, tokens, alpha=1.0):
+        """One step on the staged inputs; returns y[:tokens] (a static buffer)."""
+        if _stream_key() != self.plan_stream:
+            raise RuntimeError("this layer's plan is frozen on the stream it was created on")
+        ctx, lib = self.ctx, self.ctx.lib
+        if self.world > 1:
+            per, k = self.slots, self.top_k
+            rows, row_at = [per] * self.world, [r * per for r in range(self.world)]
+            one = lambda block, width, region: dict(blocks=[block], widths=[width] * self.world,
+                                                    col_at=[0] * self.world, total_cols=width, region=region)
+            self.peers.gather(rows, row_at, [one(self.x_in, self.model, self.regions[0]),
+                                             one(self.ids_in, k, self.regions[1]), one(self.sc_in, k, self.regions[2])])
+        N.check(lib.strix_b200_moe_plan_projections(self.plan.handle), "strix_b200_moe_plan_projections")
+        if self.world > 1:
+            self.peers.return_routes([self.each_ptr], [self.ids_all.data_ptr()], [self.valid_ptr], [self.first],
+                                     [len(self.plan.keep[2])], self.tokens_all, self.slots, self.top_k, self.model,
+                                     self.regions[3])
+            rows_ptr = self.back.data_ptr()
+        else:
+            rows_ptr = self.each_ptr
+        if tokens:
+            sd = _cur_stream()
+            N.check(lib.strix_b200_moe_combine_rows(ctx.handle, rows_ptr, self.sc_in.data_ptr(),
+                                                    self.valid_ptr + 4 * self.rank * self.slots, tokens, self.top_k,
+                                                    self.model, self.y.data_ptr(), self.model, alpha, 0.0, C.byref(sd)),
+                    "strix_b200_moe_combine_rows")
+        return self.y[:tokens]
 
     def forward(self, x, route_ids, route_scores, alpha=1.0):
-        """x [T, model] CUDA float32; route_ids [T, top_k] (global expert ids) and route_scores
-        [T, top_k] as CUDA tensors or host arrays; T <= max_tokens.  Returns y [T, model]."""
-        import torch.distributed as dist
-        ids = torch.as_tensor(np.asarray(route_ids) if not torch.is_tensor(route_ids) else route_ids).to("cuda").long()
-        scores = torch.as_tensor(np.asarray(route_scores, dtype=np.float32) if not torch.is_tensor(route_scores)
-                                 else route_scores).to("cuda", torch.float32)
-        tokens, top_k = ids.shape
-        if top_k != self.top_k or tokens * top_k > self.cap:
-            raise ValueError("routes exceed the capacity this layer was created for")
-        count = tokens * top_k
-        flat = ids.reshape(-1)
-        owner = flat // self.per_rank
-        # slot of a route in the send buffer: its owner's section, then its rank among the routes
-        # of this rank that go to the same owner, in route order (a running count per owner)
-        mine = owner[:, None] == self.rank_ids[None, :]
-        position = torch.cumsum(mine, 0).gather(1, owner[:, None]).squeeze(1) - 1
-        slot = owner * self.cap + position
-        self.send_ids.fill_(self.INVALID)
-        self.send_ids[slot] = (flat - owner * self.per_rank).int()
-        self.send_x[slot] = x.repeat_interleave(top_k, dim=0)
-        if self.world > 1:
-            dist.all_to_all_single(self.recv_x, self.send_x, group=self.group)
-            dist.all_to_all_single(self.recv_ids, self.send_ids, group=self.group)
-        self.plan.submit()
-        if self.world > 1:
-            dist.all_to_all_single(self.back, self.out_rows, group=self.group)
-        each = self.back[slot] if count else self.back[:0]
-        y = torch.empty((tokens, self.model), dtype=torch.float32, device="cuda")
-        if tokens:  # ascending slot order from +0, a zero score skips its slot: the plan's own combine
-            self.ctx.moe_combine(each.view(tokens, top_k, self.model), scores.contiguous(), y, alpha=alpha)
-        return y
+        """x [T, model] float32; route_ids [T, top_k] (global expert ids) and route_scores
+        [T, top_k] as CUDA tensors or host arrays; T <= max_tokens (T may be 0: the rank still
+        takes part in both exchanges).  Returns y [T, model]."""
+        return self.run(self.stage(x, route_ids, route_scores), alpha)
 
     def capture(self, tokens):
-        """Freezes forward() for `tokens` home tokens into a CUDA graph over static input
-        buffers.  Single-rank layers only: with the collectives inside the capture a two-rank
-        run did not return, so multi-rank forwards stay eager.  Returns
+        """Freezes run() for `tokens` home tokens into a CUDA graph (any number of ranks: the step
+        contains no library collective and nothing that allocates).  Returns
         run(x, ids, scores) -> y; y is a static buffer overwritten by the next run."""
-        if self.world != 1:
-            raise ValueError("capture is offered for single-rank layers")
-        x_in = torch.zeros((tokens, self.model), dtype=torch.float32, device="cuda")
-        ids_in = torch.zeros((tokens, self.top_k), dtype=torch.long, device="cuda")
-        sc_in = torch.zeros((tokens, self.top_k), dtype=torch.float32, device="cuda")
         stream = torch.cuda.current_stream()
-        self.forward(x_in, ids_in, sc_in)  # warm-up outside the capture
+        self.run(tokens)  # every rank warms up the same number of steps: exchanges stay paired
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            y = self.forward(x_in, ids_in, sc_in)
+            y = self.run(tokens)
 
         def run(x, ids, scores):
-            x_in.copy_(x)
-            ids_in.copy_(ids)
-            sc_in.copy_(scores)
+            self.stage(x, ids, scores)
             graph.replay()
             return y
-        self.graphs.append(graph)
+        self.graph = graph
         return run
 
     def close(self):
-        self.graphs.clear()
+        self.graph = None
         self.plan.close()
+        if self.peers:
+            self.peers.close()

@@ -160,6 +160,42 @@ def test_gemv_benchmark_shapes(ctx, bits, shape):
     w.close()
 
 
+@pytest.mark.parametrize("shape", [(128, 128), (256, 128), (16384, 128), (8192, 256), (128, 4096), (384, 19072),
+                                   (1152, 4096), (32768, 256), (33024, 128)])
+def test_gemv_one_row_fold_shapes(ctx, shape):
+    """One activation row through every way a column block can be finished: one CTA alone
+    (128x128), a block shared by more CTAs than there are decode warps (16384 -> 128: 127
+    planes gathered in rounds of sixteen), blocks that lie wholly inside a CTA's range next to
+    shared ones (384 -> 19072), the widest row the one-row kernel stages at once (32768) and one
+    block more (33024: falls back to the staged-per-segment kernel).  Each layer is submitted
+    three times on ONE plan and scratch area: the planes must come back empty every time and
+    the bits must not depend on arrival order."""
+    inputs, outputs = shape
+    bits = 2 + (inputs // 128 + outputs // 128) % 5
+    layer = synthetic.make_layer(inputs, outputs, bits, seed=4000 + inputs // 128, bias=bool(outputs % 256))
+    w = ctx.prepare(layer)
+    x = synthetic.make_activations(1, inputs, seed=4001)
+    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, bits, 2, x)
+    xd, y = dev(x), torch.zeros((1, outputs), device="cuda")
+    plan = w.plan(xd, y, N.OP_GEMV)
+    seen = None
+    for turn in range(3):
+        y.fill_(float("nan"))
+        plan.submit()
+        torch.cuda.synchronize()
+        assert ctx.device_status() == 0
+        gate(host(y), want, f"{shape} K{bits} submit {turn}")
+        seen = host(y).tobytes() if seen is None else seen
+        assert host(y).tobytes() == seen
+    # rank-1 call with alpha / beta over a poisoned and over a real old output
+    old = synthetic.rng_for(4002).normal(0, 0.3, (1, outputs)).astype(np.float32)
+    yy = dev(old.copy())
+    w.gemv(xd, yy, alpha=-0.75, beta=0.25)
+    gate(host(yy), ref.apply_alpha_beta(want, -0.75, 0.25, old), f"{shape} alpha/beta")
+    plan.close()
+    w.close()
+
+
 @pytest.mark.parametrize("shape,rows", [((4096, 129280), 1), ((16384, 4096), 8)])
 def test_gemv_tensor_parallel_layer_shapes(ctx, shape, rows):
     """The two dense layers of the tensor-parallel benchmark configuration, unsharded, K5:
@@ -238,23 +274,27 @@ def test_gemm_tensor_core_prefill_shape(ctx, bits, rows):
     w.close()
 
 
-def test_gemm_full_prefill_size_sampled_rows_and_linearity(ctx):
-    """The benchmark's largest prefill case (8192 rows, 4096 -> 12288, K4) in one launch.  The
-    CPU contract is evaluated on a sample of rows spread over all row tiles (every 331st row and
-    the last one); the whole output is checked through properties that need no reference:
-    the fused GEMV of the same rows agrees within the gates, and alpha/beta act linearly."""
-    layer = synthetic.make_layer(4096, 12288, 4, seed=500, bias=True)
-    rows = 8192
-    x = synthetic.make_activations(rows, 4096, seed=501)
+@pytest.mark.parametrize("bits,rows", [(4, 8192), (4, 2048), (5, 2048), (5, 8192), (6, 2048), (6, 8192)])
+def test_gemm_full_prefill_size_sampled_rows_and_linearity(ctx, bits, rows):
+    """The benchmark's prefill layer at full width (4096 -> 12288) in one launch, at every rate
+    and at both large row counts it is timed on.  The CPU contract is evaluated on a sample of
+    rows spread over all row tiles (every 331st row and the last one); the whole output is
+    checked through properties that need no reference: the fused GEMV of the same rows agrees
+    within the gates, and alpha/beta act linearly (the reference streams its large heads through
+    column blocks and gates them globally and per row the same way,
+    tools/make_full_head_cpu_reference.py:29-45,86-105)."""
+    layer = synthetic.make_layer(4096, 12288, bits, seed=500 + bits, bias=True)
+    x = synthetic.make_activations(rows, 4096, seed=501 + rows)
     w = ctx.prepare(layer)
     xd = dev(x)
     y = w.gemm(xd)
     torch.cuda.synchronize()
     assert ctx.device_status() == 0
     sample = sorted(set(list(range(0, rows, 331)) + [rows - 1]))
-    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, 4, 2, np.ascontiguousarray(x[sample]))
+    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, bits, 2, np.ascontiguousarray(x[sample]))
     got = host(y[sample])
-    gate(got, want, "8192-row prefill, sampled rows")
+    gate(got, want, f"K{bits} {rows}-row prefill, sampled rows")
+    assert bool(torch.isfinite(y).all())
     # the GEMV route on eight of the sampled rows: another kernel, same contract
     pick = sample[:8]
     gate(host(w.gemv(dev(np.ascontiguousarray(x[pick])))), want[:8], "gemv on sampled rows")

@@ -1,7 +1,8 @@
 """Tensor- and expert-parallel layers on the GPU.  With one GPU the ranks of a partition run
 one after another on the same device and their results are recombined with the math the
-collective performs (sum / concatenation); with two or more GPUs the same layers also run as
-one process per GPU over NCCL."""
+exchange performs (sum / concatenation); with two or more GPUs the same layers also run as
+one process per GPU, meeting through peer memory over NVLink (torch.distributed only carries
+the arena handles at set-up)."""
 import os
 import socket
 import numpy as np
@@ -113,14 +114,49 @@ def test_expert_parallel_single_rank_matches_the_block(ctx):
             w.close()
 
 
-# ---- one process per GPU over NCCL ---------------------------------------------------------
+def test_layers_follow_the_callers_stream(ctx):
+    """A plan is frozen on the stream it was created for.  A dense layer used from another
+    stream builds a plan for that stream (kernels and their consumers stay ordered); the
+    expert-parallel layer, whose step is one frozen sequence, refuses another stream."""
+    from strix_trellis_b200.tp_runtime import ExpertParallelMoE, RowParallelLinear
+    layer = synthetic.make_layer(1024, 512, 4, 9500, bias=True)
+    x = synthetic.make_activations(2, 1024, seed=9501)
+    want = oracle_linear(layer, x)
+    row = RowParallelLinear(ctx, as_tensor(layer), 0, 1)
+    xd = dev(x)
+    y = torch.zeros((2, 512), device="cuda")
+    gate(host(row.forward(xd, y)), want, "default stream")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        y.fill_(float("nan"))            # ordered before the layer only if the layer runs on `side`
+        row.forward(xd, y)
+        got = y.clone()
+    side.synchronize()
+    gate(host(got), want, "side stream")
+    assert len(row.plans) == 2
+    row.close()
+    model, inter, n_exp = 256, 128, 4
+    layers = make_experts(n_exp, model, inter, 9510)
+    ws = [tuple(ctx.prepare(l[k]) for k in ("gate", "up", "down")) for l in layers]
+    ep = ExpertParallelMoE(ctx, ws, n_exp, 0, 1, model, max_tokens=2, top_k=2)
+    with torch.cuda.stream(side):
+        with pytest.raises(RuntimeError):
+            ep.run(1)
+    ep.close()
+    for t in ws:
+        for w in t:
+            w.close()
+
+
+# ---- one process per GPU, exchanges through peer memory ---------------------------------------
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
 
 
-def _nccl_rank(rank, world, port, out):
+def _peer_rank(rank, world, port, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
     from strix_trellis_b200.runtime import Context
@@ -132,9 +168,9 @@ def _nccl_rank(rank, world, port, out):
     x = synthetic.make_activations(4, 1024, seed=9401)
     xd = torch.from_numpy(x).cuda()
     row = RowParallelLinear(ctx, as_tensor(layer), rank, world)
-    y_row = row.forward(xd).cpu().numpy()
+    y_row = [row.forward(xd).cpu().numpy() for _ in range(3)][-1]  # regions are reused with alternating parity
     col = ColumnParallelLinear(ctx, as_tensor(layer), rank, world)
-    y_col = col.forward(xd).cpu().numpy()
+    y_col = [col.forward(xd).cpu().numpy() for _ in range(3)][-1]
     model, inter, n_exp, tokens, top_k = 512, 256, 8, 6, 4
     layers = make_experts(n_exp, model, inter, 9300)
     per = -(-n_exp // world)
@@ -143,21 +179,34 @@ def _nccl_rank(rank, world, port, out):
     xm = synthetic.make_activations(tokens, model, seed=9301)
     ids, scores = synthetic.make_routes(tokens, n_exp, top_k, seed=9302)
     scores[2, 1] = 0.0
-    home = [t for t in range(tokens) if t % world == rank]  # tokens live round-robin on the ranks
-    ep = ExpertParallelMoE(ctx, ws, n_exp, rank, world, model, max_tokens=tokens, top_k=top_k)
-    y_ep = ep.forward(torch.from_numpy(xm[home]).cuda(), ids[home].astype(np.int64), scores[home]).cpu().numpy()
+    ids = ids.astype(np.int64)
+    ids[5, 1] = n_exp + 9  # an id outside the id space: that token's row must come out NaN, nothing else changes
+    slots = -(-tokens // world)
+    home = list(range(rank * slots, min(tokens, (rank + 1) * slots)))  # tokens live rank-major
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ep = ExpertParallelMoE(ctx, ws, n_exp, rank, world, model, max_tokens=slots, top_k=top_k)
+        y_ep = ep.forward(torch.from_numpy(xm[home]).cuda(), ids[home], scores[home]).cpu().numpy()
+        # the same step frozen into a graph on every rank
+        run = ep.capture(len(home))
+        y_graph = run(torch.from_numpy(xm[home]).cuda(), ids[home], scores[home]).cpu().numpy()
+        stream.synchronize()
     torch.cuda.synchronize()
     status = ctx.device_status()
-    np.savez(out + f".{rank}.npz", y_row=y_row, y_col=y_col, y_ep=y_ep, home=np.array(home), status=status)
+    np.savez(out + f".{rank}.npz", y_row=y_row, y_col=y_col, y_ep=y_ep, y_graph=y_graph, home=np.array(home),
+             status=status)
     dist.barrier()
+    ep.close()
+    row.close()
+    col.close()
     dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_over_nccl(tmp_path):
+def test_two_ranks_over_peer_memory(tmp_path):
     import torch.multiprocessing as mp
     world, out = 2, str(tmp_path / "rank")
-    mp.spawn(_nccl_rank, args=(world, _free_port(), out), nprocs=world, join=True)
+    mp.spawn(_peer_rank, args=(world, _free_port(), out), nprocs=world, join=True)
     layer = synthetic.make_layer(1024, 768, 4, 9400, bias=True)
     x = synthetic.make_activations(4, 1024, seed=9401)
     want = oracle_linear(layer, x)
@@ -167,11 +216,17 @@ def test_two_ranks_over_nccl(tmp_path):
     ids, scores = synthetic.make_routes(tokens, n_exp, top_k, seed=9302)
     scores[2, 1] = 0.0
     want_ep, _ = oracle_block(xm, layers, ids, scores, 1.0, 0.0, np.zeros((tokens, model), np.float32))
-    got_ep = np.zeros_like(want_ep)
+    got_ep, got_graph = np.zeros_like(want_ep), np.zeros_like(want_ep)
+    rows = []
     for rank in range(world):
         r = np.load(out + f".{rank}.npz")
         assert int(r["status"]) == 0
-        gate(r["y_row"], want, f"row-parallel all-reduce, rank {rank}")
-        gate(r["y_col"], want, f"column-parallel all-gather, rank {rank}")
+        gate(r["y_row"], want, f"row-parallel sum, rank {rank}")
+        gate(r["y_col"], want, f"column-parallel concatenation, rank {rank}")
+        rows.append(r["y_row"])
         got_ep[r["home"]] = r["y_ep"]
-    gate(got_ep, want_ep, "expert-parallel all-to-all", MOE_REL, MOE_NRMSE)
+        got_graph[r["home"]] = r["y_graph"]
+    assert rows[0].tobytes() == rows[1].tobytes()  # rank-ordered sum: the same bits on every rank
+    assert np.isnan(got_ep[5]).all()               # the token with an id outside the id space
+    gate(got_ep[:5], want_ep[:5], "expert-parallel block", MOE_REL, MOE_NRMSE)
+    assert got_graph[:5].tobytes() == got_ep[:5].tobytes() and np.isnan(got_graph[5]).all()
