@@ -129,7 +129,7 @@ strix_status strix_b200_moe_plan_rows(strix_tp_moe_plan plan, const float **each
  * multiples of 256) to the exchanges it runs.  A region holds two copies of an exchange's
  * payload, used alternately, so a layer may run back to back.  All ranks must issue the same
  * sequence of exchanges on a group.  A rank that never shows up makes the others give up after
- * about a second: bit 5 of the status word (strix_b200_device_status) is set and the result of
+ * several seconds: bit 5 of the status word (strix_b200_device_status) is set and the result of
  * that exchange is invalid.  `local_count` consecutive ranks starting at `first_rank` may live
  * in this process on this device: per-rank arguments are then arrays of `local_count` entries
  * (one entry in production). */

@@ -141,10 +141,12 @@ class _Transport:
     four-byte boundary, in REGIONS order; an absent bias has offset 0 and size 0."""
 
     def __init__(self, tensor):
-        if float(tensor.bits) != int(tensor.bits):
-            _fail("GPU transport v1 supports integer bitrates only")
+        # The reference keeps 1.5 / 2.5 / 3.5 off its GPU transport (container.py:152-153); this
+        # runtime decodes them on the device (mul1 only), so bits_x2 may be odd for mul1.
+        if float(tensor.bits) != int(tensor.bits) and tensor.codebook != "mul1":
+            _fail("GPU transport carries half-integer bitrates for mul1 only")
         self.fields = {"rows": tensor.output_size, "columns": tensor.input_size,
-                       "bits_x2": 2 * int(tensor.bits), "codebook": CODEBOOK_ORDER.index(tensor.codebook),
+                       "bits_x2": int(2 * float(tensor.bits)), "codebook": CODEBOOK_ORDER.index(tensor.codebook),
                        "marker": MULTIPLIER[tensor.codebook], "transport_version": 1}
         self.members = []          # (name, source array, element dtype, offset, nbytes)
         cursor = 0

@@ -46,14 +46,19 @@ strix_status geometry_check(uint64_t outputs, uint64_t inputs, uint32_t bits_x2,
                             uint32_t marker, const uint64_t (&given)[kRegionCount], LayerGeometry& g) {
     const auto dimension_ok = [](uint64_t n) { return n >= 128 && n <= INT_MAX && n % 128 == 0; };
     if (!dimension_ok(outputs) || !dimension_ok(inputs)) return STRIX_ERROR_UNSUPPORTED_FORMAT;
-    if (bits_x2 % 2 != 0 || bits_x2 < 2 || bits_x2 > 16) return STRIX_ERROR_UNSUPPORTED_FORMAT;  // integer rates 1..8
+    // integer rates 1..8 (bits_x2 even) for every codebook; 1.5 / 2.5 / 3.5 (bits_x2 3, 5, 7) for mul1
+    // only -- the reference defines them (python/strix_trellis/codec.py:12-20) but keeps them off its
+    // GPU transport (python/strix_trellis/container.py:152-153); here the device decodes them too.
+    const int rate = st::rate_code(bits_x2);
+    if (rate == 0) return STRIX_ERROR_UNSUPPORTED_FORMAT;
     bool known = false;
     if (marker_of(codebook, known) != marker || !known) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    if (st::rate_is_half(rate) && codebook != STRIX_CODEBOOK_MUL1) return STRIX_ERROR_UNSUPPORTED_FORMAT;
 #if defined(__BYTE_ORDER__) && __BYTE_ORDER__ != __ORDER_LITTLE_ENDIAN__
     return STRIX_ERROR_UNSUPPORTED_FORMAT;  // transport words are little-endian and uploaded as they are
 #endif
     uint64_t weights = 0, tile_bytes = 0;
-    if (!mul_ok(outputs, inputs, weights) || !mul_ok(weights / 8, bits_x2 / 2, tile_bytes))
+    if (!mul_ok(outputs, inputs, weights) || !mul_ok(weights / 16, bits_x2, tile_bytes))
         return STRIX_ERROR_UNSUPPORTED_FORMAT;
     const uint64_t expected[kRegionCount] = {tile_bytes, inputs * 2, outputs * 2, outputs * 4};
     for (int i = 0; i < kRegionCount; ++i) {
@@ -62,7 +67,7 @@ strix_status geometry_check(uint64_t outputs, uint64_t inputs, uint32_t bits_x2,
     }
     g.outputs = outputs;
     g.inputs = inputs;
-    g.bits = bits_x2 / 2;
+    g.bits = (uint32_t)rate;  // rate code
     g.codebook = codebook;
     g.has_bias = given[kBias] != 0;
     return STRIX_SUCCESS;

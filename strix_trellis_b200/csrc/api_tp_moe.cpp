@@ -98,7 +98,7 @@ strix_status expert_geometry(strix_context c, const strix_tp_expert_desc* expert
             dn.inputs != g.inter || dn.outputs != g.model || ga.codebook != g.codebook || up.codebook != g.codebook ||
             dn.codebook != g.codebook)
             return STRIX_ERROR_UNSUPPORTED_FORMAT;
-        g.max_bits = std::max(g.max_bits, std::max(ga.bits, std::max(up.bits, dn.bits)));
+        g.max_bits = st::heavier_rate(g.max_bits ? g.max_bits : ga.bits, st::heavier_rate(ga.bits, st::heavier_rate(up.bits, dn.bits)));
     }
     return STRIX_SUCCESS;
 }
@@ -588,7 +588,7 @@ static strix_status swiglu_shape(strix_context c, const strix_tp_swiglu_desc* d,
     s = row_view(d->input, rows, g.inputs, xs, xb);
     if (s == STRIX_SUCCESS) s = row_view(d->hidden_output, rows, g.outputs, hs, hb);
     if (s != STRIX_SUCCESS) return s;
-    const st::GroupedPlan plan = st::plan_grouped(g.inputs, g.outputs, std::max(g.bits, u.bits), 2, c->sm_count);
+    const st::GroupedPlan plan = st::plan_grouped(g.inputs, g.outputs, st::heavier_rate(g.bits, u.bits), 2, c->sm_count);
     need = st::align_up((uint64_t)2 * rows * g.outputs * 4) +
            2 * (plan.counter_bytes_per_problem + plan.partial_bytes_per_problem) + st::align_up(2 * sizeof(st::GroupedProblem));
     return STRIX_SUCCESS;
@@ -645,7 +645,7 @@ strix_status strix_tp_swiglu_plan_create(strix_context c, const strix_tp_swiglu_
     const st::DeviceWeights &g = d->gate->device, &u = d->up->device;
     p->owner = c; p->stream = cs; p->gate = d->gate; p->up = d->up; p->is_swiglu = true;
     p->rows = rows; p->inter = g.outputs; p->inputs = g.inputs; p->codebook = g.codebook;
-    p->plan = st::plan_grouped(g.inputs, g.outputs, std::max(g.bits, u.bits), 2, c->sm_count);
+    p->plan = st::plan_grouped(g.inputs, g.outputs, st::heavier_rate(g.bits, u.bits), 2, c->sm_count);
     Carver carve{static_cast<unsigned char*>(d->workspace)};
     p->g = carve.take<float>((size_t)rows * g.outputs);
     p->u = p->g + (size_t)rows * g.outputs;

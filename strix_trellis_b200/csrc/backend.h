@@ -6,11 +6,13 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include "rates.h"
+
 namespace st {
 
 // Prepared weights on the device.  `packed` holds the tiles regrouped per 128 output
-// columns: [N/128][I/16][8 column tiles][8*bits uint32 words]; a column block is one
-// contiguous stream of I*16*bits bytes.
+// columns: [N/128][I/16][8 column tiles][tile_words(rate) uint32 words]; a column block is one
+// contiguous stream of I/128 units of unit_bytes(rate) bytes.
 struct DeviceWeights {
     const uint32_t* packed;
     const uint16_t* suh;  // binary16 bits [inputs]
@@ -18,7 +20,7 @@ struct DeviceWeights {
     const float* bias;    // [outputs] or nullptr
     int inputs;
     int outputs;
-    int bits;
+    int bits;      // rate code (rates.h): 1..8 integer rates, 9..11 for 1.5 / 2.5 / 3.5
     int codebook;
 };
 

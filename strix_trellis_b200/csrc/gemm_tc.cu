@@ -294,12 +294,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                 fke = k_end_of(t);
                 const int nb = ((t / splits) / args.m_pairs) * (kBN / 128) + cb;
                 fvalid = nb < nblocks;  // a padding stripe decodes nothing
-                fcol = c.w.packed + (((size_t)(fvalid ? nb : 0) * ktiles16) * 8 + ct) * (8 * K);
+                fcol = c.w.packed + (((size_t)(fvalid ? nb : 0) * ktiles16) * 8 + ct) * tile_words(K);
             }
-            const uint32_t* tile = fcol + (size_t)fks * 4 * 8 * (8 * K);
+            const uint32_t* tile = fcol + (size_t)fks * 4 * 8 * tile_words(K);
             if (fvalid) {
 #pragma unroll
-                for (int k4 = 0; k4 < 4; ++k4) load_window<K>(tile + (size_t)k4 * 8 * (8 * K), geom, w[k4]);
+                for (int k4 = 0; k4 < 4; ++k4) load_window<K>(tile + (size_t)k4 * 8 * tile_words(K), geom, w[k4]);
             }
             ++fks;
             ++fetched;
@@ -444,6 +444,11 @@ static cudaError_t configure_gemm_tc_kernels_codebook() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<6, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<7, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<8, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+    if constexpr (CB == CB_MUL1) {
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<9, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<10, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<11, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTc);
+    }
     return e;
 }
 cudaError_t configure_gemm_tc_kernels() {
@@ -464,6 +469,13 @@ static cudaError_t launch_tc_bits(const GemmArgs& a, int grid, cudaStream_t s) {
     case 6: return launch_tc<6, CB>(a, grid, s);
     case 7: return launch_tc<7, CB>(a, grid, s);
     case 8: return launch_tc<8, CB>(a, grid, s);
+    case 9: case 10: case 11:  // 1.5 / 2.5 / 3.5 bits per weight exist for mul1 only
+        if constexpr (CB == CB_MUL1) {
+            if (a.call.w.bits == 9) return launch_tc<9, CB>(a, grid, s);
+            if (a.call.w.bits == 10) return launch_tc<10, CB>(a, grid, s);
+            return launch_tc<11, CB>(a, grid, s);
+        }
+        return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
     }
 }

@@ -259,12 +259,12 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
                 const int t = pair + flt * pairs;
                 const int nb = (t / args.m_quads) * (kBN / 128) + (int)rank;
                 fvalid = nb < nblocks;  // a padding column block decodes nothing
-                fcol = c.w.packed + (((size_t)(fvalid ? nb : 0) * ktiles16 + 2 * kh) * 8 + ct) * (8 * K);
+                fcol = c.w.packed + (((size_t)(fvalid ? nb : 0) * ktiles16 + 2 * kh) * 8 + ct) * tile_words(K);
             }
-            const uint32_t* tile = fcol + (size_t)fks * 4 * 8 * (8 * K);
+            const uint32_t* tile = fcol + (size_t)fks * 4 * 8 * tile_words(K);
             if (fvalid) {
 #pragma unroll
-                for (int k2 = 0; k2 < 2; ++k2) load_window<K>(tile + (size_t)k2 * 8 * (8 * K), geom, w[k2]);
+                for (int k2 = 0; k2 < 2; ++k2) load_window<K>(tile + (size_t)k2 * 8 * tile_words(K), geom, w[k2]);
             }
             ++fks;
             ++fetched;
@@ -343,6 +343,11 @@ static cudaError_t configure_gemm_pair_kernels_codebook() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<6, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<7, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<8, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+    if constexpr (CB == CB_MUL1) {
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<9, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<10, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_pair_kernel<11, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemP);
+    }
     return e;
 }
 cudaError_t configure_gemm_pair_kernels() {
@@ -363,6 +368,13 @@ static cudaError_t launch_pair_bits(const PairArgs& a, int grid, cudaStream_t s)
     case 6: return launch_pair<6, CB>(a, grid, s);
     case 7: return launch_pair<7, CB>(a, grid, s);
     case 8: return launch_pair<8, CB>(a, grid, s);
+    case 9: case 10: case 11:  // 1.5 / 2.5 / 3.5 bits per weight exist for mul1 only
+        if constexpr (CB == CB_MUL1) {
+            if (a.call.w.bits == 9) return launch_pair<9, CB>(a, grid, s);
+            if (a.call.w.bits == 10) return launch_pair<10, CB>(a, grid, s);
+            return launch_pair<11, CB>(a, grid, s);
+        }
+        return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
     }
 }

@@ -59,7 +59,7 @@ struct GemvArgs {
     float* partials;           // [grid][rows][128] ([grid][2][128] for the one-row kernel), every word empty on entry and on exit
 };
 
-__host__ __device__ inline int stage_bytes(int bits) { return 2048 * bits; }
+__host__ __device__ inline int stage_bytes(int rate) { return unit_bytes(rate); }
 
 }  // namespace
 
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs 
     const Range mine = cta_range(args.split, cta);
     const int my_units = mine.end - mine.begin;
     const int stages = args.stages;
-    constexpr int kStage = 2048 * K;
+    constexpr int kStage = unit_bytes(K);
 
     // shared memory: [2 x fold 8 KB][barriers 512 B][ring][core input]
     float* fold_base = reinterpret_cast<float*>(smem);
@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs 
             slot += 2;  // ring slot and use parity of this warp's next unit, without divisions
             while (slot >= stages) { slot -= stages; use ^= 1; }
             const uint32_t* tiles =
-                reinterpret_cast<const uint32_t*>(ring + (size_t)st * kStage) + ctile * (8 * K);
+                reinterpret_cast<const uint32_t*>(ring + (size_t)st * kStage) + ctile * tile_words(K);
             const uint2* bsrc = act_lane + (size_t)(resident ? hb0 + b : b) * rows * 32;
 #pragma unroll
             for (int kt = 0; kt < 8; kt += kTilesInFlight) {  // independent tiles in flight
@@ -352,7 +352,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs 
                 uint2 bf[kTilesInFlight];
 #pragma unroll
                 for (int q = 0; q < kTilesInFlight; ++q) {
-                    decode_tile_frag<K, CB>(tiles + (kt + q) * 8 * (8 * K), geom, f[q]);
+                    decode_tile_frag<K, CB>(tiles + (kt + q) * 8 * tile_words(K), geom, f[q]);
                     bf[q] = bsrc[(kt + q) * 4];
                 }
 #pragma unroll
@@ -479,7 +479,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_row_kernel(const GemvArgs ar
     const Range mine = cta_range(args.split, cta);
     const int my_units = mine.end - mine.begin;
     const int stages = args.stages;
-    constexpr int kStage = 2048 * K;
+    constexpr int kStage = unit_bytes(K);
 
     // shared memory: [2 x fold 1 KB][16 gathered planes 8 KB][flag][barriers 512 B][ring][core input]
     float* fold_base = reinterpret_cast<float*>(smem);            // [2 buffers][2 k-groups][128]
@@ -638,7 +638,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_row_kernel(const GemvArgs ar
             if (!ok) break;
             slot += 2;
             while (slot >= stages) { slot -= stages; use ^= 1; }
-            const uint32_t* tiles = reinterpret_cast<const uint32_t*>(ring + (size_t)st * kStage) + ctile * (8 * K);
+            const uint32_t* tiles = reinterpret_cast<const uint32_t*>(ring + (size_t)st * kStage) + ctile * tile_words(K);
             const uint2* bsrc = act_lane + (size_t)(hb0 + b) * 32;
 #pragma unroll
             for (int kt = 0; kt < 8; kt += kTilesInFlight) {
@@ -646,7 +646,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_row_kernel(const GemvArgs ar
                 uint2 bf[kTilesInFlight];
 #pragma unroll
                 for (int q = 0; q < kTilesInFlight; ++q) {
-                    decode_tile_frag<K, CB>(tiles + (kt + q) * 8 * (8 * K), geom, f[q]);
+                    decode_tile_frag<K, CB>(tiles + (kt + q) * 8 * tile_words(K), geom, f[q]);
                     bf[q] = bsrc[(kt + q) * 4];
                 }
 #pragma unroll
@@ -816,6 +816,13 @@ static cudaError_t launch_bits(const GemvArgs& a, int g, size_t smem, bool pdl, 
     case 6: return launch_one<6, CB>(a, g, smem, pdl, s);
     case 7: return launch_one<7, CB>(a, g, smem, pdl, s);
     case 8: return launch_one<8, CB>(a, g, smem, pdl, s);
+    case 9: case 10: case 11:  // 1.5 / 2.5 / 3.5 bits per weight exist for mul1 only
+        if constexpr (CB == CB_MUL1) {
+            if (a.call.w.bits == 9) return launch_one<9, CB>(a, g, smem, pdl, s);
+            if (a.call.w.bits == 10) return launch_one<10, CB>(a, g, smem, pdl, s);
+            if (a.call.w.bits == 11) return launch_one<11, CB>(a, g, smem, pdl, s);
+        }
+        return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
     }
 }
@@ -841,6 +848,11 @@ static cudaError_t configure_codebook() {
     if (e == cudaSuccess) e = configure_rate<6, CB>();
     if (e == cudaSuccess) e = configure_rate<7, CB>();
     if (e == cudaSuccess) e = configure_rate<8, CB>();
+    if constexpr (CB == CB_MUL1) {
+        if (e == cudaSuccess) e = configure_rate<9, CB>();
+        if (e == cudaSuccess) e = configure_rate<10, CB>();
+        if (e == cudaSuccess) e = configure_rate<11, CB>();
+    }
     return e;
 }
 cudaError_t configure_gemv_kernels() {

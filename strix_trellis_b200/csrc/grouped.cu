@@ -39,13 +39,13 @@ __device__ __forceinline__ bool consume(const unsigned char* ring, int stage_str
     uint32_t use = 0;  // ring slot and use parity of unit i, stepped without divisions
     for (int i = 0; i < nblk; ++i, st = (st + 1 == stages ? 0 : st + 1), use ^= (st == 0)) {
         if (!mbar_wait(full0 + 8 * st, use, status, kTimeoutRingFull)) return false;
-        const uint32_t* tiles = reinterpret_cast<const uint32_t*>(ring + (size_t)st * stage_stride) + warp * (8 * K);
+        const uint32_t* tiles = reinterpret_cast<const uint32_t*>(ring + (size_t)st * stage_stride) + warp * tile_words(K);
         const uint2* bsrc = act_lane + (size_t)i * rows * 32;
 #pragma unroll
         for (int kt = 0; kt < 8; kt += 2) {
             uint32_t fa[4], fb[4];
-            decode_tile_frag<K, CB>(tiles + kt * 8 * (8 * K), geom, fa);
-            decode_tile_frag<K, CB>(tiles + (kt + 1) * 8 * (8 * K), geom, fb);
+            decode_tile_frag<K, CB>(tiles + kt * 8 * tile_words(K), geom, fa);
+            decode_tile_frag<K, CB>(tiles + (kt + 1) * 8 * tile_words(K), geom, fb);
             const uint2 ba = bsrc[kt * 4], bb = bsrc[(kt + 1) * 4];
             mma_16816(acc[0], fa, ba.x, ba.y);
             mma_16816(acc[1], fb, bb.x, bb.y);
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(kThreadsG, 2) grouped_linear_kernel(const Grou
     const int hb_end = (int)((long long)hblocks * (split + 1) / args.splits);
     const int nblk = hb_end - hb_begin;
     const int stages = args.stages;
-    const int stage_bytes = 2048 * w.bits;
+    const int stage_bytes = unit_bytes(w.bits);
 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     unsigned char* ring = smem + 256;
@@ -143,7 +143,16 @@ __global__ void __launch_bounds__(kThreadsG, 2) grouped_linear_kernel(const Grou
         case 5: ok = consume<5, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
         case 6: ok = consume<6, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
         case 7: ok = consume<7, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
-        default: ok = consume<8, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
+        case 8: ok = consume<8, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc); break;
+        default:  // half-integer rates exist for mul1 only
+            if constexpr (CB == CB_MUL1) {
+                if (w.bits == 9) ok = consume<9, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc);
+                else if (w.bits == 10) ok = consume<10, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc);
+                else ok = consume<11, CB>(ring, args.stage_stride, stages, nblk, full0, empty0, act_lane, rows, warp, lane, args.status, acc);
+            } else {
+                ok = false;
+            }
+            break;
         }
         if (!ok) s_abort = 1;
         const int col = warp * 16 + (lane >> 2), r0 = 2 * (lane & 3);
@@ -199,14 +208,14 @@ GroupedPlan plan_grouped(int inputs, int outputs, int max_bits, int problems, in
         if (best < 0 || cost < best) { best = cost; splits = s; }
     }
     const int per = (hblocks + splits - 1) / splits;
-    int stages = (32 * 1024) / (2048 * max_bits);
+    int stages = (32 * 1024) / unit_bytes(max_bits);
     if (stages > per) stages = per;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 1) stages = 1;
     plan.splits = splits;
     plan.stages = stages;
     plan.ctas_per_problem = nblocks * splits;
-    plan.stage_stride = 2048 * max_bits;
+    plan.stage_stride = unit_bytes(max_bits);
     plan.smem_bytes = 256 + (size_t)stages * plan.stage_stride + (size_t)per * 256 * kGroupRows;
     plan.counter_bytes_per_problem = align_up((size_t)nblocks * sizeof(unsigned int));
     plan.partial_bytes_per_problem = align_up((size_t)nblocks * splits * kGroupRows * 128 * sizeof(float));

@@ -100,7 +100,9 @@ __device__ __forceinline__ void exchange_signal(const PeerView& v, const Turn& t
         st_release_sys(&there->flags[t.parity()][t.rank][blockIdx.x], t.epoch);
     }
 }
-// Step 4, bounded: about a second, then the status word says so and the CTA skips its reads.
+// Step 4, bounded: ranks of one job may be seconds apart on the host (one of them loading or
+// checking something), so the limit is several seconds, far beyond any exchange that is going
+// to complete; then the status word says so and the CTA skips its reads.
 __device__ __forceinline__ bool exchange_wait(const PeerView& v, const Turn& t) {
     __shared__ int s_late;
     if (threadIdx.x == 0) s_late = 0;
@@ -108,7 +110,7 @@ __device__ __forceinline__ bool exchange_wait(const PeerView& v, const Turn& t) 
     if ((int)threadIdx.x < v.world) {
         const uint32_t* flag = &t.mine->flags[t.parity()][threadIdx.x][blockIdx.x];
         bool seen = false;
-        for (uint32_t tries = 0; tries < (1u << 20) && !seen; ++tries) seen = ld_acquire_sys(flag) == t.epoch;
+        for (uint32_t tries = 0; tries < (1u << 23) && !seen; ++tries) seen = ld_acquire_sys(flag) == t.epoch;
         if (!seen) {
             if (v.status) atomicOr(v.status, kTimeoutPeer);
             s_late = 1;

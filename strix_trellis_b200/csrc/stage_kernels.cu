@@ -26,7 +26,7 @@ __global__ void regroup_kernel(const uint32_t* __restrict__ src, uint32_t* __res
 
 cudaError_t launch_regroup(const uint32_t* src, uint32_t* dst, int inputs, int outputs, int bits,
                            cudaStream_t stream) {
-    const int ktiles = inputs / 16, ntiles = outputs / 16, words = 8 * bits;
+    const int ktiles = inputs / 16, ntiles = outputs / 16, words = tile_words(bits);
     const long long total = (long long)ktiles * ntiles * words;
     const int block = 256;
     const long long want = (total + block - 1) / block;
@@ -36,7 +36,7 @@ cudaError_t launch_regroup(const uint32_t* src, uint32_t* dst, int inputs, int o
 }
 
 __device__ __forceinline__ const uint32_t* tile_ptr(const DeviceWeights& w, int kt, int nt) {
-    const int words = 8 * w.bits, ktiles = w.inputs / 16;
+    const int words = tile_words(w.bits), ktiles = w.inputs / 16;
     return w.packed + (((long long)(nt >> 3) * ktiles + kt) * 8 + (nt & 7)) * words;
 }
 
@@ -73,6 +73,14 @@ static cudaError_t dequantize_bits(const DeviceWeights& w, uint16_t* q, int grid
     case 6: dequantize_kernel<6, CB><<<grid, 256, 0, s>>>(w, q); break;
     case 7: dequantize_kernel<7, CB><<<grid, 256, 0, s>>>(w, q); break;
     case 8: dequantize_kernel<8, CB><<<grid, 256, 0, s>>>(w, q); break;
+    case 9: case 10: case 11:  // 1.5 / 2.5 / 3.5 bits per weight exist for mul1 only
+        if constexpr (CB == CB_MUL1) {
+            if (w.bits == 9) dequantize_kernel<9, CB><<<grid, 256, 0, s>>>(w, q);
+            else if (w.bits == 10) dequantize_kernel<10, CB><<<grid, 256, 0, s>>>(w, q);
+            else dequantize_kernel<11, CB><<<grid, 256, 0, s>>>(w, q);
+            break;
+        }
+        return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
@@ -220,6 +228,14 @@ static cudaError_t core_exact_bits(const DeviceWeights& w, const uint16_t* a, in
     case 6: core_exact_kernel<6, CB><<<grid, 256, 0, s>>>(w, a, rows, c); break;
     case 7: core_exact_kernel<7, CB><<<grid, 256, 0, s>>>(w, a, rows, c); break;
     case 8: core_exact_kernel<8, CB><<<grid, 256, 0, s>>>(w, a, rows, c); break;
+    case 9: case 10: case 11:  // 1.5 / 2.5 / 3.5 bits per weight exist for mul1 only
+        if constexpr (CB == CB_MUL1) {
+            if (w.bits == 9) core_exact_kernel<9, CB><<<grid, 256, 0, s>>>(w, a, rows, c);
+            else if (w.bits == 10) core_exact_kernel<10, CB><<<grid, 256, 0, s>>>(w, a, rows, c);
+            else core_exact_kernel<11, CB><<<grid, 256, 0, s>>>(w, a, rows, c);
+            break;
+        }
+        return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

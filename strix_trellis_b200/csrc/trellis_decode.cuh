@@ -14,23 +14,39 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include "rates.h"
+
 namespace st {
 
 enum : int { CB_3INST = 0, CB_MCG = 1, CB_MUL1 = 2 };
 
 // ---- ring geometry of a lane's window (all compile-time in K, run-time in lane) ---
 template <int K> struct Ring {
-    static constexpr int kWords = 8 * K;    // uint32 words per tile
-    static constexpr int kBits = 256 * K;   // ring length
-    // A lane's eight windows span 16+7K bits starting at bit ((8l+1)K-16) mod ring.
-    static constexpr int kSpan = 16 + 7 * K;
-    // Worst-case in-word offset is 31 for odd K; the offsets of even K are listed in
-    // the comment of lane_offset().  Words needed = ceil((offset + span)/32).
-    static constexpr int kLoadWords = (K <= 4) ? 2 : 3;
-    __device__ static __forceinline__ int start_bit(int lane) {
-        return ((8 * lane + 1) * K - 16 + kBits) % kBits;
+    static constexpr bool kHalf = rate_is_half(K);
+    static constexpr int kLow = kHalf ? K - 8 : K;  // bits of an even stream position
+    static constexpr int kWords = tile_words(K);    // uint32 words per tile
+    static constexpr int kBits = 32 * kWords;       // ring length
+    static constexpr int kLaneBits = kBits / 32;    // bits the eight positions of one lane consume
+    // Offset of state j's window from state 0's: j positions of kLow bits plus one extra bit for
+    // every odd position passed (half rates).
+    __host__ __device__ static constexpr int field_pos(int j) { return j * kLow + (kHalf ? (j + 1) / 2 : 0); }
+    // A lane's eight windows span field_pos(7)+16 bits starting at bit (lane*kLaneBits + kLow - 16)
+    // mod ring.  Two ring words suffice when the largest in-word offset any lane has plus that span
+    // stays within 64 bits (rates 1..4, 1.5 and 2.5); the others need three.
+    static constexpr int kSpan = field_pos(7) + 16;
+    __host__ __device__ static constexpr int start_bit(int lane) {
+        return (lane * kLaneBits + kLow - 16 + kBits) % kBits;
     }
+    __host__ __device__ static constexpr int max_offset() {
+        int most = 0;
+        for (int lane = 0; lane < 32; ++lane) most = (start_bit(lane) & 31) > most ? (start_bit(lane) & 31) : most;
+        return most;
+    }
+    static constexpr int kLoadWords = (max_offset() + kSpan <= 64) ? 2 : 3;
 };
+static_assert(Ring<1>::kLoadWords == 2 && Ring<3>::kLoadWords == 2 && Ring<4>::kLoadWords == 2 &&
+              Ring<5>::kLoadWords == 3 && Ring<8>::kLoadWords == 3 && Ring<9>::kLoadWords == 2 &&
+              Ring<10>::kLoadWords == 2 && Ring<11>::kLoadWords == 3, "window words");
 
 // Per-lane constants of the window: word indices (with ring wrap) and the in-word bit
 // offset.  Computed once per thread, outside every loop.
@@ -129,10 +145,11 @@ __device__ __forceinline__ void extract_states(const uint32_t (&w)[3], const Lan
                 }
         }
     } else {
-        s[0] = field16<0 * K>(a); s[1] = field16<1 * K>(a);
-        s[2] = field16<2 * K>(a); s[3] = field16<3 * K>(a);
-        s[4] = field16<4 * K>(a); s[5] = field16<5 * K>(a);
-        s[6] = field16<6 * K>(a); s[7] = field16<7 * K>(a);
+        using R = Ring<K>;
+        s[0] = field16<R::field_pos(0)>(a); s[1] = field16<R::field_pos(1)>(a);
+        s[2] = field16<R::field_pos(2)>(a); s[3] = field16<R::field_pos(3)>(a);
+        s[4] = field16<R::field_pos(4)>(a); s[5] = field16<R::field_pos(5)>(a);
+        s[6] = field16<R::field_pos(6)>(a); s[7] = field16<R::field_pos(7)>(a);
     }
 }
 

@@ -74,9 +74,10 @@ class Weights:
         trellis = np.asarray(layer.trellis)
         self.inputs, self.outputs = trellis.shape[0] * 16, trellis.shape[1] * 16
         bits = float(layer.bits)
-        if not bits.is_integer():
-            raise ValueError("GPU transport supports integer bitrates only")
-        self.bits, self.codebook = int(bits), layer.codebook
+        if (2 * bits) != int(2 * bits) or not (bits.is_integer() or layer.codebook == "mul1"):
+            raise ValueError("rates are 1..8, and 1.5 / 2.5 / 3.5 for mul1")
+        self.bits, self.codebook = (int(bits) if bits.is_integer() else bits), layer.codebook
+        self.bits_x2 = int(2 * bits)
         keep = []
         t, tp, tb = _bytes_view(trellis.view(np.uint16) if trellis.dtype.itemsize == 2 else trellis, "<u2")
         su, sup, sub = _bytes_view(layer.suh, "<f2")
@@ -102,7 +103,7 @@ class Weights:
             m.struct_size = C.sizeof(N.Metadata)
             m.transport_version = 1
             m.rows, m.columns = self.outputs, self.inputs
-            m.bits_x2, m.codebook, m.marker = self.bits * 2, cb, N.MARKERS[self.codebook]
+            m.bits_x2, m.codebook, m.marker = self.bits_x2, cb, N.MARKERS[self.codebook]
             m.trellis_offset, m.trellis_bytes = offsets[0], tb
             m.suh_offset, m.suh_bytes = offsets[1], sub
             m.svh_offset, m.svh_bytes = offsets[2], svb
@@ -120,7 +121,7 @@ class Weights:
             d = N.PartsDesc()
             d.struct_size = C.sizeof(N.PartsDesc)
             d.abi_version, d.transport_version = N.ABI_VERSION, 1
-            d.bits_x2, d.rows, d.columns = self.bits * 2, self.outputs, self.inputs
+            d.bits_x2, d.rows, d.columns = self.bits_x2, self.outputs, self.inputs
             d.codebook, d.marker = cb, N.MARKERS[self.codebook]
             d.trellis, d.suh, d.svh = N.HostRegion(tp, tb), N.HostRegion(sup, sub), N.HostRegion(svp, svb)
             d.bias = N.HostRegion(bp, bb)

@@ -21,7 +21,7 @@ class Layer:
     suh: np.ndarray          # float16 [I]
     svh: np.ndarray          # float16 [N]
     bias: np.ndarray | None  # float32 [N]
-    bits: int
+    bits: float  # 1..8, or 1.5 / 2.5 / 3.5 (mul1)
     codebook: str
 
     @property
@@ -50,7 +50,7 @@ def make_layer(inputs, outputs, bits, seed=BASE_SEED, codebook="mul1", bias=Fals
     if inputs % 128 or outputs % 128:
         raise ValueError("dimensions must be multiples of 128")
     rng = rng_for(seed)
-    trellis = rng.integers(0, 65536, (inputs // 16, outputs // 16, 16 * bits), dtype=np.uint16)
+    trellis = rng.integers(0, 65536, (inputs // 16, outputs // 16, int(16 * bits)), dtype=np.uint16)
     suh = sign_scale(rng, inputs, sigma)
     svh = sign_scale(rng, outputs, sigma)
     b = rng.normal(0.0, 0.01, outputs).astype(np.float32) if bias else None

@@ -69,7 +69,7 @@ def test_output_stage_folds_split_planes_in_order(ctx):
     acc = np.zeros((3, 256), np.float32)
     for s in range(5):
         acc = acc + planes[s]
-    want = c_oracle.output_stages(acc, layer.svh, layer.bias)["output"]
+    want = c_oracle.output_stages(acc, layer.svh, layer.bias)["output_fp32"]
     assert host(w.output_stages(dev(planes))).tobytes() == want.tobytes()
     w.close()
 
@@ -209,6 +209,38 @@ def test_gemv_tensor_parallel_layer_shapes(ctx, shape, rows):
     gate(host(w.gemv(dev(x))), want, f"K5 {shape} rows {rows}")
     assert ctx.device_status() == 0
     w.close()
+
+
+def test_half_integer_rates_decode_bit_exact_and_multiply(ctx, golden_dir):
+    """Rates 1.5 / 2.5 / 3.5 (stream positions alternate between floor(rate) and one bit more,
+    mul1 only; reference python/strix_trellis/codec.py:12-20, CPU-only there).  The decoded Q of
+    the golden tiles carries the hash the reference's own decoder produced; a larger layer goes
+    through the one-row kernel, the multi-row kernel, the 8-row chunks and the tensor-core GEMM
+    against the NumPy contract."""
+    meta = json.loads((golden_dir / "half_rates.json").read_text())
+    rng = synthetic.rng_for(synthetic.BASE_SEED + 50)
+    ones = np.ones(128, np.float16)
+    for rate in (1.5, 2.5, 3.5):
+        t = rng.integers(0, 65536, (8, 8, int(16 * rate)), dtype=np.uint16)
+        w = ctx.prepare(synthetic.Layer(t, ones, ones, None, rate, "mul1"))
+        assert sha(host(w.dequantize())) == meta[str(rate)]["q"]
+        w.close()
+        layer = synthetic.make_layer(512, 384, rate, seed=7000 + int(rate * 2), bias=True)
+        x = synthetic.make_activations(100, 512, seed=7001)
+        want = ref.linear_stages(x, layer.trellis, layer.suh, layer.svh, rate, "mul1", layer.bias)["output_fp32"]
+        w = ctx.prepare(layer)
+        assert host(w.dequantize()).tobytes() == ref.dequantize(layer.trellis, rate, "mul1").tobytes()
+        for rows in (1, 3, 8):
+            gate(host(w.gemv(dev(x[:rows]))), want[:rows], f"rate {rate} gemv rows {rows}")
+        for rows in (20, 100):
+            gate(host(w.gemm(dev(x[:rows]))), want[:rows], f"rate {rate} gemm rows {rows}")
+        _, _, core_in = w.input_stages(dev(x[:2]))
+        exact = w.output_stages(w.core_exact(core_in))
+        assert host(exact).tobytes() == want[:2].tobytes()  # reference accumulation order: identical bits
+        assert ctx.device_status() == 0
+        w.close()
+    with pytest.raises((ValueError, N.StrixError)):  # half-integer rates exist for mul1 only
+        ctx.prepare(synthetic.Layer(t, ones, ones, None, 3.5, "mcg"))
 
 
 def test_config1_against_reference_golden(ctx, golden_dir):
