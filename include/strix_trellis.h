@@ -59,8 +59,9 @@ typedef enum strix_status {
 
 typedef enum strix_dtype {
     STRIX_DTYPE_INVALID = 0,
-    STRIX_DTYPE_F16 = 1, /* reserved, rejected */
-    STRIX_DTYPE_BF16 = 2, /* reserved, rejected */
+    STRIX_DTYPE_F16 = 1,  /* reserved and rejected by the reference (include/strix_trellis.h:62); honoured here */
+    STRIX_DTYPE_BF16 = 2, /* for the tensors of gemv / gemm / linear plans / TP dense plans: widened exactly on load, */
+                          /* rounded to nearest even on store; the arithmetic in between is the float32 contract */
     STRIX_DTYPE_F32 = 3
 } strix_dtype;
 

@@ -149,9 +149,10 @@ strix_status strix_b200_peer_group_create(strix_context context, void *const *lo
                                           uint32_t world, strix_b200_peer_group *out);
 strix_status strix_b200_peer_group_destroy(strix_b200_peer_group group);
 
-/* rows[i] (count floats, count % 4 == 0, 16-byte aligned) of every rank is replaced by the sum
- * over ranks, added in ascending rank order from +0: identical bits on every rank.  Region
- * size: 2 * world * count * 4 bytes. */
+/* rows[i] (count floats, count even, 8-byte aligned) of every rank is replaced by the sum over
+ * ranks, added in ascending rank order from +0: identical bits on every rank.  Meant for the
+ * few rows a decode step produces: every value travels with its own arrival mark, which
+ * doubles the bytes and removes a round trip.  Region size: 2 * world * count * 8 bytes. */
 strix_status strix_b200_peer_sum(strix_b200_peer_group group, float *const *rows, uint64_t count,
                                  uint64_t region, const strix_stream *stream);
 
@@ -217,14 +218,14 @@ strix_status strix_b200_peer_return_routes(strix_b200_peer_group group,
  * library holds that array until the process exits).  It calls no allocating routine.
  *
  * Same operator and same results as strix_gemv (rows 0..8); desc->workspace must be
- * NULL/0; tensors are still the caller's.  Limits: outputs <= STRIX_B200_NOALLOC_MAX_OUTPUTS
- * and at most 192 SMs; anything larger returns STRIX_ERROR_INSUFFICIENT_BUFFER.
+ * NULL/0; tensors are still the caller's.  Limit: the array holds one partial plane per
+ * persistent CTA and activation row, enough for eight rows on a device of up to 256 SMs; a
+ * launch that would need more returns STRIX_ERROR_INSUFFICIENT_BUFFER.
  * The first call on a device looks up the array's device address (one runtime query);
  * make that first call before starting any stream capture.  All calls on a device share
  * the one array, so two calls that can overlap on the GPU (different streams without an
  * ordering between them) race; keep them in one stream or order them with events. */
-#define STRIX_B200_NOALLOC_MAX_OUTPUTS UINT64_C(524288)
-#define STRIX_B200_NOALLOC_SCRATCH_BYTES UINT64_C(1589248)
+#define STRIX_B200_NOALLOC_SCRATCH_BYTES UINT64_C(1048576)
 strix_status strix_b200_gemv_noalloc(strix_context context, const strix_matmul_desc *desc,
                                      const strix_stream *stream);
 

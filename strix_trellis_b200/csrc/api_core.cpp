@@ -70,11 +70,21 @@ strix_status device_buffer(strix_context c, const void* p, uint64_t bytes, uint6
 }
 
 // ---- tensors ----------------------------------------------------------------------
+// The reference reserves STRIX_DTYPE_F16 / BF16 and refuses them (include/strix_trellis.h:39-40,
+// 62-63); here activations of either type are widened exactly on load and outputs rounded to
+// nearest even on store, with the float32 contract in between.
 static strix_status tensor_check(const strix_tensor_desc& t, uint64_t width, uint32_t rank,
-                                 uint64_t rows, bool contiguous, uint64_t& stride, uint64_t& bytes) {
+                                 uint64_t rows, bool contiguous, uint64_t& stride, uint64_t& bytes, int& dtype) {
     const strix_status s = header(&t);
     if (s != STRIX_SUCCESS) return s;
-    if (enum_bits(t.dtype) != STRIX_DTYPE_F32 || t.rank != rank) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    switch (enum_bits(t.dtype)) {
+    case STRIX_DTYPE_F32: dtype = st::DT_F32; break;
+    case STRIX_DTYPE_F16: dtype = st::DT_F16; break;
+    case STRIX_DTYPE_BF16: dtype = st::DT_BF16; break;
+    default: return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    }
+    if (t.rank != rank) return STRIX_ERROR_UNSUPPORTED_FORMAT;
+    const uint64_t element = st::dtype_bytes(dtype);
     if (rank == 1) {
         if (t.shape[0] != width || t.shape[1] || t.strides[0] != 1 || t.strides[1])
             return STRIX_ERROR_UNSUPPORTED_FORMAT;
@@ -93,10 +103,10 @@ static strix_status tensor_check(const strix_tensor_desc& t, uint64_t width, uin
             return STRIX_ERROR_INVALID_ARGUMENT;
         elements += width;
     }
-    if (!mul_ok(elements, sizeof(float), bytes) || !range_ok(t.data, bytes))
+    if (!mul_ok(elements, element, bytes) || !range_ok(t.data, bytes))
         return STRIX_ERROR_INVALID_ARGUMENT;
     if (bytes > t.buffer_bytes) return STRIX_ERROR_INSUFFICIENT_BUFFER;
-    if (bytes && (!t.data || reinterpret_cast<uintptr_t>(t.data) % alignof(float)))
+    if (bytes && (!t.data || reinterpret_cast<uintptr_t>(t.data) % element))
         return STRIX_ERROR_INVALID_ARGUMENT;
     return STRIX_SUCCESS;
 }
@@ -112,9 +122,9 @@ strix_status view_check(strix_context c, const strix_matmul_desc* d, bool contig
     const uint64_t rows = rank == 1 ? 1 : d->input.shape[0];
     if (rows > INT_MAX) return STRIX_ERROR_UNSUPPORTED_FORMAT;
     v.rows = static_cast<int>(rows);
-    s = tensor_check(d->input, (uint64_t)w.inputs, rank, rows, contiguous, v.x_stride, v.x_bytes);
+    s = tensor_check(d->input, (uint64_t)w.inputs, rank, rows, contiguous, v.x_stride, v.x_bytes, v.x_dtype);
     if (s != STRIX_SUCCESS) return s;
-    s = tensor_check(d->output, (uint64_t)w.outputs, rank, rows, contiguous, v.y_stride, v.y_bytes);
+    s = tensor_check(d->output, (uint64_t)w.outputs, rank, rows, contiguous, v.y_stride, v.y_bytes, v.y_dtype);
     if (s != STRIX_SUCCESS) return s;
     const strix_weights_impl* wi = d->weights;
     if (overlap(d->input.data, v.x_bytes, d->output.data, v.y_bytes) ||
@@ -129,6 +139,8 @@ st::LinearCall make_call(strix_context c, const strix_matmul_desc& d, const View
     call.w = d.weights->device;
     call.x = static_cast<const float*>(d.input.data);
     call.y = static_cast<float*>(d.output.data);
+    call.x_dtype = v.x_dtype;
+    call.y_dtype = v.y_dtype;
     call.rows = v.rows;
     call.x_stride = (long long)v.x_stride;
     call.y_stride = (long long)v.y_stride;
@@ -173,9 +185,9 @@ strix_status storage_check(strix_context c, const strix_matmul_desc& d, const Vi
         overlap(workspace, bytes, wi->allocation, wi->allocation_bytes))
         return STRIX_ERROR_INVALID_ARGUMENT;
     if (!v.rows) return STRIX_SUCCESS;  // empty call: no device inspection at all
-    strix_status s = device_buffer(c, d.input.data, v.x_bytes, alignof(float));
+    strix_status s = device_buffer(c, d.input.data, v.x_bytes, st::dtype_bytes(v.x_dtype));
     if (s != STRIX_SUCCESS) return s;
-    s = device_buffer(c, d.output.data, v.y_bytes, alignof(float));
+    s = device_buffer(c, d.output.data, v.y_bytes, st::dtype_bytes(v.y_dtype));
     if (s != STRIX_SUCCESS) return s;
     return device_buffer(c, workspace, bytes, kAlign);
 }

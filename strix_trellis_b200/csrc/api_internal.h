@@ -97,6 +97,7 @@ struct View {
     int rows = 0;
     uint64_t x_stride = 0, y_stride = 0;
     uint64_t x_bytes = 0, y_bytes = 0;  // accessed span, row gaps included
+    int x_dtype = st::DT_F32, y_dtype = st::DT_F32;  // element types (st::DT_*)
 };
 // contiguous = the strix_gemv / strix_gemm tensor rules; otherwise TP row views.
 strix_status view_check(strix_context c, const strix_matmul_desc* d, bool contiguous, View& v);

@@ -24,11 +24,20 @@ struct DeviceWeights {
     int codebook;
 };
 
-// Row views: element (r, c) of x is x[r * x_stride + c]; likewise y.
+// Element types of activation and output tensors.  F16 and BF16 inputs are widened to float32
+// when they are read (exact), outputs are rounded to nearest even when they are stored; the
+// arithmetic in between is the float32 contract.
+enum : int { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
+inline size_t dtype_bytes(int dtype) { return dtype == DT_F32 ? 4 : 2; }
+
+// Row views: element (r, c) of x is element r * x_stride + c of the buffer at `x` (of type
+// x_dtype, so `x` is a float pointer only when x_dtype is DT_F32); likewise y.
 struct LinearCall {
     DeviceWeights w;
     const float* x;
     float* y;
+    int x_dtype = DT_F32;
+    int y_dtype = DT_F32;
     int rows;
     long long x_stride;
     long long y_stride;

@@ -27,8 +27,10 @@ cudaError_t launch_gemm_chunked(const LinearCall& call, int sm_count, void* work
     for (int begin = 0; begin < call.rows; begin += 8) {
         LinearCall part = call;
         part.rows = call.rows - begin < 8 ? call.rows - begin : 8;
-        part.x = call.x + (long long)begin * call.x_stride;
-        part.y = call.y + (long long)begin * call.y_stride;
+        part.x = reinterpret_cast<const float*>(reinterpret_cast<const unsigned char*>(call.x) +
+                                                (size_t)begin * call.x_stride * dtype_bytes(call.x_dtype));
+        part.y = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(call.y) +
+                                          (size_t)begin * call.y_stride * dtype_bytes(call.y_dtype));
         const GemvPlan g = plan_gemv(call.w, part.rows, sm_count);
         if (!zeroed) {  // the first chunk is the largest: its scratch covers the others'
             const cudaError_t e = reset_gemv_scratch(workspace, g, stream);

@@ -49,7 +49,7 @@ struct GemmArgs {
 }  // namespace
 
 // ---- launch 1: input stages into pre-swizzled A tiles ------------------------------------
-__global__ void input_tiles_kernel(const float* __restrict__ x, long long x_stride,
+__global__ void input_tiles_kernel(const float* __restrict__ x, int x_dtype, long long x_stride,
                                    const uint16_t* __restrict__ suh, int inputs, int rows, int rows_padded,
                                    unsigned char* __restrict__ a_tiles) {
     const int lane = threadIdx.x & 31;
@@ -63,7 +63,7 @@ __global__ void input_tiles_kernel(const float* __restrict__ x, long long x_stri
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int c = blk * 128 + lane + 32 * j;
-                v[j] = __half2float(scale_input(x[(long long)row * x_stride + c], suh[c]));
+                v[j] = __half2float(scale_input(load_element(x, x_dtype, (long long)row * x_stride + c), suh[c]));
             }
             hadamard128_warp(v, lane);
         }
@@ -247,14 +247,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                             for (int u = 0; u < 4; ++u) {
                                 const int row = row_base + r4 + u;
                                 if (row < c.rows) {
-                                    float* out = c.y + (long long)row * c.y_stride + nb * 128 + lane;
+                                    const long long out = (long long)row * c.y_stride + nb * 128 + lane;
 #pragma unroll
                                     for (int j = 0; j < 4; ++j) {
                                         float value = __fmul_rn(v[u][j], sv[j]);
                                         if (c.w.bias) value = __fadd_rn(value, bi[j]);
-                                        value = __fmul_rn(value, c.alpha);
-                                        if (c.beta != 0.0f) value = __fadd_rn(value, __fmul_rn(c.beta, out[32 * j]));
-                                        out[32 * j] = value;
+                                        scale_and_store(c.y, c.y_dtype, out + 32 * j, value, c.alpha, c.beta);
                                     }
                                 }
                             }
@@ -352,7 +350,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
 // order from +0 and apply the output stages; one warp per (row, 128-column block) ------------
 __global__ void splitk_finish_kernel(const float* __restrict__ partials, int splits, size_t plane, int rows,
                                      int outputs, const uint16_t* __restrict__ svh, const float* __restrict__ bias,
-                                     float alpha, float beta, float* y, long long y_stride) {
+                                     float alpha, float beta, float* y, int y_dtype, long long y_stride) {
     const int lane = threadIdx.x & 31;
     const int nblocks = outputs / 128;
     const long long items = (long long)rows * nblocks;
@@ -369,8 +367,9 @@ __global__ void splitk_finish_kernel(const float* __restrict__ partials, int spl
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int cidx = nb * 128 + lane + 32 * j;
-            float* out = y + (long long)row * y_stride + cidx;
-            *out = finish_output(v[j], svh[cidx], bias, cidx, alpha, beta, out);
+            float value = __fmul_rn(v[j], half_bits_to_float(svh[cidx]));
+            if (bias) value = __fadd_rn(value, bias[cidx]);
+            scale_and_store(y, y_dtype, (long long)row * y_stride + cidx, value, alpha, beta);
         }
     }
 }
@@ -490,7 +489,7 @@ cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* work
         const long long groups = (long long)rows_padded * (call.w.inputs / 128);
         const long long want = (groups + 7) / 8;
         const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
-        input_tiles_kernel<<<grid, 256, 0, stream>>>(call.x, call.x_stride, call.w.suh, call.w.inputs, call.rows,
+        input_tiles_kernel<<<grid, 256, 0, stream>>>(call.x, call.x_dtype, call.x_stride, call.w.suh, call.w.inputs, call.rows,
                                                      rows_padded, static_cast<unsigned char*>(workspace));
         const cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
@@ -518,7 +517,7 @@ cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* work
     const long long want = (items + 7) / 8;
     splitk_finish_kernel<<<(int)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(
         args.partials, plan.k_splits, (size_t)rows_padded * call.w.outputs, call.rows, call.w.outputs, call.w.svh,
-        call.w.bias, call.alpha, call.beta, call.y, call.y_stride);
+        call.w.bias, call.alpha, call.beta, call.y, call.y_dtype, call.y_stride);
     return cudaGetLastError();
 }
 

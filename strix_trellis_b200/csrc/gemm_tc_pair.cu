@@ -221,14 +221,12 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
                             for (int u = 0; u < 4; ++u) {
                                 const int row = row_base + r4 + u;
                                 if (row < c.rows) {
-                                    float* out = c.y + (long long)row * c.y_stride + nb * 128 + lane;
+                                    const long long out = (long long)row * c.y_stride + nb * 128 + lane;
 #pragma unroll
                                     for (int j = 0; j < 4; ++j) {
                                         float value = __fmul_rn(v[u][j], sv[j]);
                                         if (c.w.bias) value = __fadd_rn(value, bi[j]);
-                                        value = __fmul_rn(value, c.alpha);
-                                        if (c.beta != 0.0f) value = __fadd_rn(value, __fmul_rn(c.beta, out[32 * j]));
-                                        out[32 * j] = value;
+                                        scale_and_store(c.y, c.y_dtype, out + 32 * j, value, c.alpha, c.beta);
                                     }
                                 }
                             }

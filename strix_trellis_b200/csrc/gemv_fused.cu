@@ -110,12 +110,9 @@ __device__ __forceinline__ void fold_row(const GemvArgs& args, const float* own,
     hadamard128_warp(v, lane);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        float* out = c.y + (long long)r * c.y_stride + nb * 128 + lane + 32 * j;
         float value = __fmul_rn(v[j], sv[j]);
         if (c.w.bias) value = __fadd_rn(value, bs[j]);
-        value = __fmul_rn(value, c.alpha);
-        if (c.beta != 0.0f) value = __fadd_rn(value, __fmul_rn(c.beta, *out));
-        *out = value;
+        scale_and_store(c.y, c.y_dtype, (long long)r * c.y_stride + nb * 128 + lane + 32 * j, value, c.alpha, c.beta);
     }
 }
 
@@ -277,12 +274,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const GemvArgs 
                 if (item < n) {
                     int hb;
                     where(item, rr[u], hb, ss[u]);
-                    const float* xr = c.x + (long long)rr[u] * c.x_stride + (size_t)hb * 128;
+                    const long long xr = (long long)rr[u] * c.x_stride + (long long)hb * 128;
                     const uint16_t* su = c.w.suh + (size_t)hb * 128;
                     const bool ready = first_scales_ready && item == warp;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        xv[u][j] = xr[lane + 32 * j];
+                        xv[u][j] = load_element(c.x, c.x_dtype, xr + lane + 32 * j);
                         sc[u][j] = ready ? su_first[j] : su[lane + 32 * j];
                     }
                 }
@@ -561,12 +558,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_row_kernel(const GemvArgs ar
             hadamard128_warp(v, lane);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float* out = c.y + nb * 128 + lane + 32 * j;
                 float value = __fmul_rn(v[j], sv[j]);
                 if (c.w.bias) value = __fadd_rn(value, bs[j]);
-                value = __fmul_rn(value, c.alpha);
-                if (c.beta != 0.0f) value = __fadd_rn(value, __fmul_rn(c.beta, *out));
-                *out = value;
+                scale_and_store(c.y, c.y_dtype, (long long)nb * 128 + lane + 32 * j, value, c.alpha, c.beta);
             }
             asm volatile("bar.arrive %0, %1;" ::"r"(4 + buf), "r"(kDumpThreads) : "memory");
             ++flush;
@@ -590,7 +584,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_row_kernel(const GemvArgs ar
     float xv[4] = {0.f, 0.f, 0.f, 0.f};
     if (warp < need) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) xv[j] = c.x[(size_t)my_hb * 128 + lane + 32 * j];
+        for (int j = 0; j < 4; ++j) xv[j] = load_element(c.x, c.x_dtype, (long long)my_hb * 128 + lane + 32 * j);
     }
 
     bool ok = true;
@@ -610,7 +604,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_row_kernel(const GemvArgs ar
         } else {  // more blocks than warps: the rest comes straight from memory
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                v[j] = __half2float(scale_input(c.x[(size_t)hb * 128 + lane + 32 * j], c.w.suh[(size_t)hb * 128 + lane + 32 * j]));
+                v[j] = __half2float(scale_input(load_element(c.x, c.x_dtype, (long long)hb * 128 + lane + 32 * j),
+                                                c.w.suh[(size_t)hb * 128 + lane + 32 * j]));
         }
         hadamard128_warp(v, lane);
 #pragma unroll
@@ -736,12 +731,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_row_kernel(const GemvArgs ar
             hadamard128_warp(v, lane);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float* out = c.y + nb * 128 + lane + 32 * j;
                 float value = __fmul_rn(v[j], sv[j]);
                 if (c.w.bias) value = __fadd_rn(value, bs[j]);
-                value = __fmul_rn(value, c.alpha);
-                if (c.beta != 0.0f) value = __fadd_rn(value, __fmul_rn(c.beta, *out));
-                *out = value;
+                scale_and_store(c.y, c.y_dtype, (long long)nb * 128 + lane + 32 * j, value, c.alpha, c.beta);
             }
         }
     }

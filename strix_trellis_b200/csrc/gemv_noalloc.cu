@@ -1,6 +1,6 @@
 // strix_b200_gemv_noalloc: the fused decode GEMV for callers that cannot supply or
-// obtain scratch memory.  The split-K scratch (partial planes)
-// lives in a fixed array inside the library image instead of a caller workspace.
+// obtain scratch memory.  The split-K scratch (the partial planes of one launch) lives in a
+// fixed array inside the library image instead of a caller workspace.
 #include <mutex>
 
 #include "api_internal.h"
@@ -9,16 +9,14 @@ using namespace sapi;
 
 namespace {
 
-// Layout: [reserved: kMaxColumnBlocks x u32][partial planes: kMaxCtas x 2 x 8 rows
-// x 128 floats].  Every GPU that loads the library carries this array until exit.
-constexpr size_t kMaxColumnBlocks = STRIX_B200_NOALLOC_MAX_OUTPUTS / 128;
-constexpr size_t kMaxCtas = 192;  // persistent CTAs (one per SM); B200 has 148
-constexpr size_t kCounterBytes = kMaxColumnBlocks * sizeof(unsigned int);
-constexpr size_t kPlaneBytes = kMaxCtas * 2 * 8 * 128 * sizeof(float);
-static_assert(kCounterBytes % 256 == 0, "planes must stay 256-byte aligned");
-static_assert(kCounterBytes + kPlaneBytes == STRIX_B200_NOALLOC_SCRATCH_BYTES, "header out of date");
+// The whole array is partial planes, starting at offset 0: one plane of 128 floats per
+// persistent CTA and activation row (the one-row kernel keeps two half planes per CTA).  A
+// launch runs at most one CTA per SM, so 1 MiB covers eight rows on a device of up to 256 SMs
+// (a B200 has 148).  Every GPU that loads the library carries this array until exit.
+constexpr size_t kScratchBytes = STRIX_B200_NOALLOC_SCRATCH_BYTES;
+static_assert(kScratchBytes == 256 * 8 * 128 * sizeof(float), "header out of date");
 
-static __device__ __align__(256) unsigned char g_scratch[kCounterBytes + kPlaneBytes];
+static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 
 // In host code `g_scratch` is only a handle for the runtime, not an address a kernel
 // could use; the device address is looked up once per device and cached here.
@@ -56,9 +54,9 @@ extern "C" strix_status strix_b200_gemv_noalloc(strix_context c, const strix_mat
     if (s != STRIX_SUCCESS || !v.rows) return s;
     const st::DeviceWeights& w = d->weights->device;
     const st::GemvPlan plan = st::plan_gemv(w, v.rows, c->sm_count);
-    // Beyond the built-in scratch: refuse, never fall back to an allocation.
-    if (c->device >= kMaxDevices || plan.counter_bytes > kCounterBytes || plan.partial_bytes > kPlaneBytes ||
-        (uint64_t)w.outputs > STRIX_B200_NOALLOC_MAX_OUTPUTS)
+    // Beyond the built-in scratch (more CTAs x rows than the array has planes for): refuse, never
+    // fall back to an allocation.
+    if (c->device >= kMaxDevices || plan.counter_bytes + plan.partial_bytes > kScratchBytes)
         return STRIX_ERROR_INSUFFICIENT_BUFFER;
     void* scratch = nullptr;
     cudaError_t e = scratch_address(c->device, &scratch);
@@ -67,6 +65,6 @@ extern "C" strix_status strix_b200_gemv_noalloc(strix_context c, const strix_mat
     // word empty, an aborted one may not, so the planes are marked empty before every call.
     e = st::reset_gemv_scratch(scratch, plan, cs);
     if (e != cudaSuccess) return cuda_status(e);
-    // launch_gemv places the planes right after plan.counter_bytes, inside the array
+    // launch_gemv places the planes at the start of the array
     return cuda_status(st::launch_gemv(make_call(c, *d, v), plan, scratch, c->programmatic_launch, cs));
 }

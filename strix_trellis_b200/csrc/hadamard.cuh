@@ -4,8 +4,11 @@
 // is written with a non-contractable intrinsic (__fmul_rn/__fadd_rn/__fsub_rn), so
 // the result does not depend on -fmad.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
+
+#include "backend.h"
 
 namespace st {
 
@@ -47,6 +50,26 @@ __device__ __forceinline__ float half_bits_to_float(uint16_t h) {
 // round differently on ties (reference tests/test_numerics.py:46-54).
 __device__ __forceinline__ __half scale_input(float x, uint16_t suh) {
     return __float2half_rn(__fmul_rn(x, half_bits_to_float(suh)));
+}
+
+// Element `index` of a tensor of `dtype` as float32 (exact widening), and the store of a
+// float32 result into one (round to nearest even).
+__device__ __forceinline__ float load_element(const void* base, int dtype, long long index) {
+    if (dtype == DT_F32) return static_cast<const float*>(base)[index];
+    const uint16_t bits = static_cast<const uint16_t*>(base)[index];
+    return dtype == DT_F16 ? __half2float(__ushort_as_half(bits)) : __uint_as_float((uint32_t)bits << 16);
+}
+__device__ __forceinline__ void store_element(void* base, int dtype, long long index, float value) {
+    if (dtype == DT_F32) static_cast<float*>(base)[index] = value;
+    else if (dtype == DT_F16) static_cast<__half*>(base)[index] = __float2half_rn(value);
+    else static_cast<__nv_bfloat16*>(base)[index] = __float2bfloat16_rn(value);
+}
+// The tail of the output stages on a finished value: + bias was done by the caller; alpha, beta
+// over the old element (never read when beta is zero of either sign), store.
+__device__ __forceinline__ void scale_and_store(void* y, int dtype, long long index, float value, float alpha, float beta) {
+    value = __fmul_rn(value, alpha);
+    if (beta != 0.0f) value = __fadd_rn(value, __fmul_rn(beta, load_element(y, dtype, index)));
+    store_element(y, dtype, index, value);
 }
 
 // alpha * (had * svh + bias) + beta * old, each step rounded on its own; beta == 0

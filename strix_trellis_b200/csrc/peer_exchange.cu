@@ -125,36 +125,51 @@ __device__ __forceinline__ void exchange_end(const Turn& t) {
 }
 
 // ---- sum of the ranks' rows ------------------------------------------------------------------
+// Small payloads (one to eight rows of a projection's output) are all latency, so this exchange
+// does without the flag step: every value travels as an 8-byte word {value, epoch} (8-byte
+// stores are not torn), a receiver spins on the words themselves, and the data is there the
+// moment it can be trusted -- one NVLink hop instead of payload, fence, flag.  The parities of
+// the region alternate as for the other exchanges.
 struct ReduceArgs {
     PeerView view;
-    float* rows[kRanks];         // per local rank: `count4` float4, replaced by the sum
-    long long count4;
-    unsigned long long region;   // byte offset in every arena: [2 parities][world][count4] float4
+    float* rows[kRanks];         // per local rank: `count2` pairs of floats, replaced by the sum
+    long long count2;
+    unsigned long long region;   // byte offset in every arena: [2 parities][world][count2] x 16 bytes
 };
+__device__ __forceinline__ void st_sys_v4(uint4* p, uint4 v) {
+    asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 __global__ void __launch_bounds__(kThreads) peer_sum_kernel(const ReduceArgs a) {
+    __shared__ int s_late;
     const Turn t = exchange_begin(a.view);
-    uint4* y = reinterpret_cast<uint4*>(a.rows[blockIdx.y]);
+    if (threadIdx.x == 0) s_late = 0;
+    float2* y = reinterpret_cast<float2*>(a.rows[blockIdx.y]);
     const long long lane0 = (long long)blockIdx.x * kThreads + threadIdx.x, step = (long long)kCtas * kThreads;
-    const long long slot0 = (long long)(a.region / 16) + (long long)t.parity() * a.view.world * a.count4;
-    for (long long i = lane0; i < a.count4; i += step) {
-        const uint4 value = y[i];
+    const long long slot0 = (long long)(a.region / 16) + (long long)t.parity() * a.view.world * a.count2;
+    for (long long i = lane0; i < a.count2; i += step) {
+        const float2 value = y[i];
+        const uint4 word = make_uint4(__float_as_uint(value.x), t.epoch, __float_as_uint(value.y), t.epoch);
         for (int p = 0; p < a.view.world; ++p)
-            reinterpret_cast<uint4*>(a.view.arena[p])[slot0 + (long long)t.rank * a.count4 + i] = value;
+            st_sys_v4(reinterpret_cast<uint4*>(a.view.arena[p]) + slot0 + (long long)t.rank * a.count2 + i, word);
     }
-    exchange_signal(a.view, t);
-    if (exchange_wait(a.view, t)) {
-        const uint4* slots = reinterpret_cast<const uint4*>(a.view.arena[t.rank]) + slot0;
-        for (long long i = lane0; i < a.count4; i += step) {
-            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;  // ascending rank order from +0, on every rank
-            for (int r = 0; r < a.view.world; ++r) {
-                const uint4 part = ld_sys_v4(slots + (long long)r * a.count4 + i);
-                s0 = __fadd_rn(s0, __uint_as_float(part.x));
-                s1 = __fadd_rn(s1, __uint_as_float(part.y));
-                s2 = __fadd_rn(s2, __uint_as_float(part.z));
-                s3 = __fadd_rn(s3, __uint_as_float(part.w));
+    const uint4* slots = reinterpret_cast<const uint4*>(a.view.arena[t.rank]) + slot0;
+    bool late = false;
+    for (long long i = lane0; i < a.count2 && !late; i += step) {
+        float s0 = 0.f, s1 = 0.f;  // ascending rank order from +0, on every rank
+        for (int r = 0; r < a.view.world && !late; ++r) {
+            uint4 part = ld_sys_v4(slots + (long long)r * a.count2 + i);
+            for (uint32_t tries = 0; (part.y != t.epoch || part.w != t.epoch) && !late; ++tries) {
+                if (tries >= (1u << 23)) late = true;  // bounded: several seconds
+                else part = ld_sys_v4(slots + (long long)r * a.count2 + i);
             }
-            y[i] = make_uint4(__float_as_uint(s0), __float_as_uint(s1), __float_as_uint(s2), __float_as_uint(s3));
+            s0 = __fadd_rn(s0, __uint_as_float(part.x));
+            s1 = __fadd_rn(s1, __uint_as_float(part.z));
         }
+        if (!late) y[i] = make_float2(s0, s1);
+    }
+    if (late) {
+        if (a.view.status) atomicOr(a.view.status, kTimeoutPeer);
+        s_late = 1;
     }
     exchange_end(t);
 }
@@ -371,15 +386,15 @@ strix_status strix_b200_peer_sum(strix_b200_peer_group g, float* const* rows, ui
     cudaStream_t cs{};
     const strix_status s = group_call(g, stream, cs);
     if (s != STRIX_SUCCESS) return s;
-    if (!rows || count % 4 || count > (1ull << 40)) return STRIX_ERROR_INVALID_ARGUMENT;
+    if (!rows || count % 2 || count > (1ull << 40)) return STRIX_ERROR_INVALID_ARGUMENT;
     if (!count) return STRIX_SUCCESS;
-    if (!region_fits(g, region, 2ull * g->view.world * count * 4)) return STRIX_ERROR_INSUFFICIENT_BUFFER;
+    if (!region_fits(g, region, 2ull * g->view.world * count * 8)) return STRIX_ERROR_INSUFFICIENT_BUFFER;
     ReduceArgs a{};
     a.view = g->view;
-    a.count4 = (long long)(count / 4);
+    a.count2 = (long long)(count / 2);
     a.region = region;
     for (int i = 0; i < g->local_count; ++i) {
-        if (!rows[i] || reinterpret_cast<uintptr_t>(rows[i]) % 16) return STRIX_ERROR_INVALID_ARGUMENT;
+        if (!rows[i] || reinterpret_cast<uintptr_t>(rows[i]) % 8) return STRIX_ERROR_INVALID_ARGUMENT;
         a.rows[i] = rows[i];
     }
     peer_sum_kernel<<<dim3(kCtas, g->local_count), kThreads, 0, cs>>>(a);

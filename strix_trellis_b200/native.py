@@ -12,7 +12,7 @@ ABI_VERSION = 1
 ALIGN = 256
 MARKERS = {"3inst": 0, "mcg": 0xCBAC1FED, "mul1": 0x83DCD12D}
 CODEBOOKS = ("3inst", "mcg", "mul1")
-DTYPE_F32 = 3
+DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 1, 2, 3
 OP_GEMV, OP_GEMM = 0, 1
 
 STATUS_NAMES = ["SUCCESS", "INVALID_ARGUMENT", "ABI_MISMATCH", "UNSUPPORTED_FORMAT",
@@ -276,13 +276,13 @@ def stream_desc(cuda_stream=0):
     return s
 
 
-def tensor_desc(ptr, nbytes, shape, strides=None):
+def tensor_desc(ptr, nbytes, shape, strides=None, dtype=None):
     t = TensorDesc()
     t.struct_size = C.sizeof(TensorDesc)
     t.abi_version = ABI_VERSION
     t.data = ptr or None
     t.buffer_bytes = nbytes
-    t.dtype = DTYPE_F32
+    t.dtype = DTYPE_F32 if dtype is None else dtype
     t.rank = len(shape)
     if len(shape) == 1:
         t.shape[0], t.shape[1] = shape[0], 0

@@ -148,8 +148,10 @@ class Weights:
         for t, desc_name, width in ((x, "input", self.inputs), (y, "output", self.outputs)):
             shape = tuple(t.shape)
             strides = None if t.dim() == 1 else (t.stride(0), t.stride(1))
-            nbytes = 0 if t.numel() == 0 else ((shape[0] - 1) * t.stride(0) + shape[-1]) * 4 if t.dim() == 2 else t.numel() * 4
-            setattr(d, desc_name, N.tensor_desc(t.data_ptr() if t.numel() else 0, nbytes, shape, strides))
+            size = t.element_size()
+            nbytes = 0 if t.numel() == 0 else ((shape[0] - 1) * t.stride(0) + shape[-1]) * size if t.dim() == 2 else t.numel() * size
+            dtype = {torch.float32: N.DTYPE_F32, torch.float16: N.DTYPE_F16, torch.bfloat16: N.DTYPE_BF16}[t.dtype]
+            setattr(d, desc_name, N.tensor_desc(t.data_ptr() if t.numel() else 0, nbytes, shape, strides, dtype))
         d.alpha, d.beta = alpha, beta
         if workspace is not None and workspace.numel():
             d.workspace, d.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
@@ -166,6 +168,7 @@ class Weights:
         return torch.empty(max(n, 1), dtype=torch.uint8, device=x.device) if n else None
 
     def gemv(self, x, y=None, alpha=1.0, beta=0.0, workspace=None, stream=None):
+        """x, y: float32, float16 or bfloat16 CUDA tensors (each on its own); y defaults to float32."""
         if y is None:
             y = torch.empty(x.shape[:-1] + (self.outputs,), dtype=torch.float32, device=x.device)
         if workspace is None:

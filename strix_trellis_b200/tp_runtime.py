@@ -47,7 +47,7 @@ class RowParallelLinear:
         """The exchange arena, set up (collectively: every rank must get here) at the first
         forward; `local` alone never needs it."""
         if self.peers is None:
-            payload = self.world * self.max_rows * self.weights.outputs * 4
+            payload = self.world * self.max_rows * self.weights.outputs * 8  # every value travels with its arrival mark
             self.peers = PeerGroup(self.ctx, 2 * payload + 4096, self.rank, self.world, self.group)
             self.region = self.peers.reserve(payload)
         return self.peers

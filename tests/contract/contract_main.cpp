@@ -303,7 +303,23 @@ void call_and_plan_rules(strix_context c) {
             std::memcpy(side ? &d.output.dtype : &d.input.dtype, &raw, sizeof raw);
             refuse(STRIX_ERROR_UNSUPPORTED_FORMAT);
         }
-    d.input.dtype = STRIX_DTYPE_BF16; refuse(STRIX_ERROR_UNSUPPORTED_FORMAT);
+    d.input.dtype = STRIX_DTYPE_INVALID; refuse(STRIX_ERROR_UNSUPPORTED_FORMAT);
+    {   // binary16 / bfloat16 tensors: two bytes per element in the span and alignment rules
+        d.input.dtype = STRIX_DTYPE_BF16;
+        d.output.dtype = STRIX_DTYPE_F16;
+        d.input.buffer_bytes = 2 * 128 * 2;   // exactly two rows of 128 elements
+        d.output.buffer_bytes = 2 * 256 * 2;
+        CHECK(strix_gemv(c, &d, &stream) == STRIX_SUCCESS);
+        CHECK(record().last.x_dtype == st::DT_BF16 && record().last.y_dtype == st::DT_F16);
+        d.input.buffer_bytes -= 1;
+        CHECK(strix_gemv(c, &d, &stream) == STRIX_ERROR_INSUFFICIENT_BUFFER);
+        d.input.buffer_bytes += 1;
+        d.output.data = static_cast<char*>(y) + 2;  // two-byte alignment suffices
+        CHECK(strix_gemv(c, &d, &stream) == STRIX_SUCCESS);
+        d.output.data = static_cast<char*>(y) + 1;
+        CHECK(strix_gemv(c, &d, &stream) == STRIX_ERROR_INVALID_ARGUMENT);
+        d = good;
+    }
     const float bad_scalars[] = {std::numeric_limits<float>::infinity(), -std::numeric_limits<float>::infinity(),
                                  std::numeric_limits<float>::quiet_NaN()};
     for (float v : bad_scalars) {

@@ -69,7 +69,7 @@ def test_output_stage_folds_split_planes_in_order(ctx):
     acc = np.zeros((3, 256), np.float32)
     for s in range(5):
         acc = acc + planes[s]
-    want = c_oracle.output_stages(acc, layer.svh, layer.bias)["output_fp32"]
+    want = c_oracle.output_stages(acc, layer.svh, layer.bias)["output"]
     assert host(w.output_stages(dev(planes))).tobytes() == want.tobytes()
     w.close()
 
@@ -219,10 +219,10 @@ def test_half_integer_rates_decode_bit_exact_and_multiply(ctx, golden_dir):
     against the NumPy contract."""
     meta = json.loads((golden_dir / "half_rates.json").read_text())
     rng = synthetic.rng_for(synthetic.BASE_SEED + 50)
-    ones = np.ones(128, np.float16)
+    ones, more_ones = np.ones(128, np.float16), np.ones(128, np.float16)  # two regions may not share bytes
     for rate in (1.5, 2.5, 3.5):
         t = rng.integers(0, 65536, (8, 8, int(16 * rate)), dtype=np.uint16)
-        w = ctx.prepare(synthetic.Layer(t, ones, ones, None, rate, "mul1"))
+        w = ctx.prepare(synthetic.Layer(t, ones, more_ones, None, rate, "mul1"))
         assert sha(host(w.dequantize())) == meta[str(rate)]["q"]
         w.close()
         layer = synthetic.make_layer(512, 384, rate, seed=7000 + int(rate * 2), bias=True)
@@ -240,7 +240,50 @@ def test_half_integer_rates_decode_bit_exact_and_multiply(ctx, golden_dir):
         assert ctx.device_status() == 0
         w.close()
     with pytest.raises((ValueError, N.StrixError)):  # half-integer rates exist for mul1 only
-        ctx.prepare(synthetic.Layer(t, ones, ones, None, 3.5, "mcg"))
+        ctx.prepare(synthetic.Layer(t, ones, more_ones, None, 3.5, "mcg"))
+
+
+@pytest.mark.parametrize("rows", [1, 5, 24, 300])
+def test_half_precision_tensors_widen_on_load_and_round_on_store(ctx, rows):
+    """binary16 / bfloat16 activations and outputs (reserved and refused by the reference,
+    include/strix_trellis.h:39-40; honoured here).  The arithmetic is the float32 contract: an
+    input of either type gives the bits of the same values passed as float32, and an output of
+    either type is the float32 output rounded to nearest even -- through the one-row kernel, the
+    multi-row kernel, the 8-row chunks and the tensor-core GEMM, with and without alpha / beta
+    over an old output of that type."""
+    layer = synthetic.make_layer(1024, 640, 4, seed=8100 + rows, bias=True)
+    w = ctx.prepare(layer)
+    run = w.gemv if rows <= 8 else w.gemm
+    x32 = synthetic.make_activations(rows, 1024, seed=8101)  # binary16-representable values
+    want32 = host(run(dev(x32)))
+    gate(want32, c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, 4, 2, x32), "float32 tensors")
+    for dtype in (torch.float16, torch.bfloat16):
+        xin = dev(x32).to(dtype)                       # bfloat16 drops bits: compare against the widened values
+        base = run(xin.to(torch.float32))
+        y32 = run(xin)
+        assert torch.equal(y32, base), dtype           # widening on load is exact
+        y = torch.empty((rows, 640), dtype=dtype, device="cuda")
+        run(xin, y)
+        assert torch.equal(y, base.to(dtype)), dtype   # one rounding, to nearest even
+        old = (torch.randn((rows, 640), device="cuda") * 0.25).to(dtype)
+        y2 = old.clone()
+        run(xin, y2, alpha=-0.75, beta=0.5)
+        expect = (base * -0.75 + old.to(torch.float32) * 0.5).to(dtype)  # each product rounded, then the sum, then the store
+        assert torch.equal(y2, expect), dtype
+    # a strided float16 row view through a tensor-parallel dense plan
+    if rows <= 8:
+        from strix_trellis_b200.runtime import DensePlan
+        wide = torch.zeros((rows, 1536), dtype=torch.float16, device="cuda")
+        wide[:, 256:1280] = dev(x32).to(torch.float16)
+        out = torch.zeros((rows, 1024), dtype=torch.bfloat16, device="cuda")
+        plan = DensePlan(w, wide[:, 256:1280], out[:, 128:768])
+        plan.submit()
+        torch.cuda.synchronize()
+        assert torch.equal(out[:, 128:768], torch.from_numpy(want32).cuda().to(torch.bfloat16))
+        assert float(out[:, :128].abs().max()) == 0.0 and float(out[:, 768:].abs().max()) == 0.0
+        plan.close()
+    assert ctx.device_status() == 0
+    w.close()
 
 
 def test_config1_against_reference_golden(ctx, golden_dir):
@@ -405,8 +448,9 @@ def test_rejections_with_the_real_driver(ctx):
     d.alpha = float("inf")
     assert status(d) == N.INVALID_ARGUMENT
     d = w.matmul_desc(x, y, workspace=ws)
-    d.input.dtype = 1
-    assert status(d) == N.UNSUPPORTED_FORMAT
+    for bad_dtype in (0, 7):  # 1, 2, 3 are binary16, bfloat16, float32
+        d.input.dtype = bad_dtype
+        assert status(d) == N.UNSUPPORTED_FORMAT
     torch.cuda.synchronize()
     assert (host(y) == 7.0).all()  # nothing ran
     # and the deep-K global-scratch path itself is correct

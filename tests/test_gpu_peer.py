@@ -28,7 +28,7 @@ def ctx():
 def test_sum_is_rank_ordered_and_identical_on_every_rank(ctx, world):
     g = PeerGroup(ctx, 4 << 20, rank=0, world=world, local_ranks=world)
     count = 8 * 4096
-    region = g.reserve(world * count * 4)
+    region = g.reserve(world * count * 8)
     rng = np.random.default_rng(70 + world)
     for turn in range(5):  # parities alternate; regions are reused
         parts = (rng.normal(size=(world, count)) * 10.0 ** rng.integers(-3, 4, (world, count))).astype(np.float32)
