@@ -119,6 +119,21 @@ def cpu_baseline(seconds_budget=12.0):
             "sample": f"{calls} whole K4 R1 layers of shapes (1152,4096),(4096,4096) in {dt:.1f} s"}, dt / max(calls, 1)
 
 
+def numpy_baseline():
+    """The NumPy restatement of the reference's CPU path (vectorised decode + staged float32
+    contract) on one 1152 x 4096 K4 layer, one row, one process: the figure the reference's own
+    Python model would give on this host."""
+    from oracle import trellis_ref as ref
+    from strix_trellis_b200 import synthetic
+    layer = synthetic.make_layer(1152, 4096, BITS, seed=synthetic.BASE_SEED + 2)
+    x = synthetic.make_activations(ROWS, 1152)
+    t0 = time.perf_counter()
+    ref.linear_stages(x, layer.trellis, layer.suh, layer.svh, BITS, "mul1", None)
+    dt = time.perf_counter() - t0
+    return {"value": layer.packed_bytes / dt / 1e9, "unit": "GB/s", "cores": 1,
+            "sample": f"one 1152x4096 K4 R1 layer through oracle/trellis_ref.py in {dt:.2f} s"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -468,6 +483,21 @@ def run_case(args):
         us = time_calls(torch, stream, one_pass, 3, warm=1) / len(plans)
         print(json.dumps({"case": "gemv 4096x14336 K4 R1", "us_per_launch": round(us, 2),
                           "GBps": round(layer.packed_bytes / us / 1e3, 1), "status": ctx.device_status()}))
+    elif args.case == "decode":
+        # the decoder's own ceiling: decode + mma on tiles resident in shared memory, no memory traffic
+        out = {"case": "decode-rate probe, 16 warps per SM, tiles in shared memory"}
+        sm = torch.cuda.get_device_properties(0).multi_processor_count
+        mhz = float(subprocess.run(["nvidia-smi", "--id=0", "--query-gpu=clocks.max.sm", "--format=csv,noheader,nounits"],
+                                   capture_output=True, text=True).stdout.strip() or 0)
+        for bits in (2, 3, 4, 5, 6):
+            w = ctx.prepare(synthetic.make_layer(1024, 1024, bits, seed=synthetic.BASE_SEED + 900 + bits))
+            clk = w.decode_rate(400)
+            out[f"K{bits}"] = {"clocks_per_tile_per_subpartition": round(clk, 1),
+                               "GBps_ceiling_at_max_clock": round(4 * sm * mhz * 1e6 / clk * 32 * bits / 1e9, 0)}
+            w.close()
+        out["sm_max_mhz"] = mhz
+        out["status"] = ctx.device_status()
+        print(json.dumps(out))
     elif args.case == "gemm":
         print(json.dumps({"case": "gemm 4096->12288 K4", **gemm_case(torch, ctx, stream, [2048], reps=2),
                           "status": ctx.device_status()}))
@@ -704,12 +734,14 @@ def run_gpu(args):
         traffic = None
         # DRAM bytes per packed weight byte of this kernel, from the committed ncu summary of
         # the 4096x14336 case; traffic grows in proportion to the packed bytes of a launch
-        tpath = ROOT / "profiles" / "gemv_fused_k4_r1_4096x14336.md"
+        tpath = ROOT / "profiles" / "gemv_row_k4_4096x14336.md"
         if tpath.exists():
             for text in tpath.read_text().splitlines():
                 if text.strip().startswith("dram_bytes_per_packed_byte"):
                     traffic = float(text.split("=")[1])
         base, _ = cpu_baseline() if world == 1 else (None, None)
+        if base is not None:
+            base["numpy_reference"] = numpy_baseline()
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
@@ -722,7 +754,7 @@ def run_gpu(args):
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_kind": peak_kind,
                          "traffic": None if traffic is None else round(traffic * total_bytes / launches),
-                         "kernel": "gemv_fused_kernel<4, mul1, one row>",
+                         "kernel": "gemv_row_kernel<4, mul1>",
                          "algorithmic_bytes_per_launch": round(total_bytes / launches)},
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
@@ -744,7 +776,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the GEMM / MoE / TP side measurements")
-    ap.add_argument("--case", choices=["gemv", "gemm", "moe"], help="run one small profiling workload and exit")
+    ap.add_argument("--case", choices=["gemv", "gemm", "moe", "decode"], help="run one small profiling workload and exit")
     args = ap.parse_args()
     if args.case:
         run_case(args)

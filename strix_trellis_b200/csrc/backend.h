@@ -74,6 +74,11 @@ cudaError_t launch_output_stages(const DeviceWeights& w, const float* core /*[sp
 cudaError_t launch_core_exact(const DeviceWeights& w, const uint16_t* core16 /*[rows][I]*/, int rows,
                               float* core_out /*[rows][N]*/, cudaStream_t stream);
 
+// Decode-rate probe: the GEMV's inner loop (decode + mma) on tiles resident in shared memory,
+// `iters` passes over two units on `grid` CTAs of 16 warps; clocks[b] = SM clocks of CTA b.
+cudaError_t launch_decode_rate(const DeviceWeights& w, int iters, int grid, float* sink, long long* clocks,
+                               cudaStream_t stream);
+
 // ---- decode GEMV, rows 1..8, everything fused ---------------------------------------
 struct GemvPlan {
     int grid;            // persistent CTAs (one per SM, fewer for tiny layers)

@@ -4,6 +4,7 @@
 // and transforms (the approach of the reference harness, docs/GPU_TESTS.md:97-109).
 #include "backend.h"
 #include "hadamard.cuh"
+#include "sync_primitives.cuh"
 #include "trellis_decode.cuh"
 
 namespace st {
@@ -239,6 +240,85 @@ static cudaError_t core_exact_bits(const DeviceWeights& w, const uint16_t* a, in
     default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
+}
+
+// ---- decode-rate probe ---------------------------------------------------------------------
+// The inner loop of the fused GEMV with nothing around it: two units of the layer's weights sit
+// in shared memory, sixteen warps (column tile = warp % 8, two warps per tile taking turns)
+// decode them `iters` times with the production device function and feed every tile to the same
+// mma as the GEMV.  No global traffic, no barriers, no fold: the clocks per tile measured here
+// are the instruction-issue cost of the decoder itself, i.e. the ceiling of every kernel that
+// decodes (what the reference measured with modes 0-4 of src/microbench.hip for its own decoder).
+namespace {
+constexpr int kProbeWarps = 16;
+constexpr int kProbeUnits = 2;
+}
+template <int K, int CB>
+__global__ void __launch_bounds__(kProbeWarps * 32) decode_rate_kernel(const DeviceWeights w, int iters, float* sink,
+                                                                       long long* clocks) {
+    extern __shared__ uint32_t probe_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int kUnitWords = unit_bytes(K) / 4;
+    const long long have = (long long)w.inputs * w.outputs / 256 * tile_words(K);  // words in the packed stream
+    for (int i = threadIdx.x; i < kProbeUnits * kUnitWords; i += blockDim.x) probe_smem[i] = w.packed[i % have];
+    __syncthreads();
+    const LaneGeom<K> geom(lane);
+    const uint32_t b0 = 0x3C003C00u, b1 = 0x3C003800u;  // fixed activation fragments
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const long long t0 = clock64();
+    for (int it = 0; it < iters; ++it) {
+        const uint32_t* tiles = probe_smem + (it & (kProbeUnits - 1)) * kUnitWords + (warp & 7) * tile_words(K);
+#pragma unroll
+        for (int kt = 0; kt < 8; kt += 2) {
+            uint32_t fa[4], fb[4];
+            decode_tile_frag<K, CB>(tiles + kt * 8 * tile_words(K), geom, fa);
+            decode_tile_frag<K, CB>(tiles + (kt + 1) * 8 * tile_words(K), geom, fb);
+            mma_16816(acc[0], fa, b0, b1);
+            mma_16816(acc[1], fb, b0, b1);
+        }
+    }
+    const long long t1 = clock64();
+    sink[blockIdx.x * blockDim.x + threadIdx.x] =
+        acc[0][0] + acc[0][1] + acc[0][2] + acc[0][3] + acc[1][0] + acc[1][1] + acc[1][2] + acc[1][3];
+    if (threadIdx.x == 0) clocks[blockIdx.x] = t1 - t0;
+}
+
+template <int CB>
+static cudaError_t decode_rate_bits(const DeviceWeights& w, int iters, float* sink, long long* clocks, int grid,
+                                    cudaStream_t s) {
+    const size_t smem = (size_t)kProbeUnits * unit_bytes(w.bits);
+    switch (w.bits) {
+    case 1: decode_rate_kernel<1, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
+    case 2: decode_rate_kernel<2, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
+    case 3: decode_rate_kernel<3, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
+    case 4: decode_rate_kernel<4, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
+    case 5: decode_rate_kernel<5, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
+    case 6: decode_rate_kernel<6, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
+    case 7: decode_rate_kernel<7, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
+    case 8: decode_rate_kernel<8, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
+    case 9: case 10: case 11:
+        if constexpr (CB == CB_MUL1) {
+            if (w.bits == 9) decode_rate_kernel<9, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks);
+            else if (w.bits == 10) decode_rate_kernel<10, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks);
+            else decode_rate_kernel<11, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks);
+            break;
+        }
+        return cudaErrorInvalidValue;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+// sink: grid * 512 floats, clocks: grid int64 (device memory); clocks[b] = SM clocks CTA b spent in the loop
+cudaError_t launch_decode_rate(const DeviceWeights& w, int iters, int grid, float* sink, long long* clocks,
+                               cudaStream_t stream) {
+    if (iters < 1 || grid < 1) return cudaErrorInvalidValue;
+    switch (w.codebook) {
+    case CB_3INST: return decode_rate_bits<CB_3INST>(w, iters, sink, clocks, grid, stream);
+    case CB_MCG: return decode_rate_bits<CB_MCG>(w, iters, sink, clocks, grid, stream);
+    case CB_MUL1: return decode_rate_bits<CB_MUL1>(w, iters, sink, clocks, grid, stream);
+    default: return cudaErrorInvalidValue;
+    }
 }
 
 cudaError_t launch_core_exact(const DeviceWeights& w, const uint16_t* core16, int rows, float* core_out,
