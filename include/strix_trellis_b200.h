@@ -126,6 +126,12 @@ strix_status strix_b200_moe_plan_projections(strix_tp_moe_plan plan);
 strix_status strix_b200_moe_plan_rows(strix_tp_moe_plan plan, const float **each,
                                       const int32_t **row_valid);
 
+/* Diagnostics: the gate and up projection rows that strix_tp_moe_plan_gate_up left in plan
+ * memory, F32 [tokens * top_k][intermediate] each, before SwiGLU combined them into the
+ * hidden rows at the start of the caller's workspace. */
+strix_status strix_b200_moe_plan_gate_up_rows(strix_tp_moe_plan plan, const float **gate,
+                                              const float **up);
+
 /* ---- exchange between the ranks of one node through peer memory over NVLink -----------------
  * The shard-boundary steps of the tensor- and expert-parallel layers as single kernels that
  * store straight into the other ranks' memory: no library collective, no host

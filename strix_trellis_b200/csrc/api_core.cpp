@@ -169,7 +169,8 @@ cudaError_t enqueue_linear(strix_context c, const st::LinearCall& call, void* wo
         }
         return st::launch_gemv(call, p, workspace, c->programmatic_launch, stream);
     }
-    return st::launch_gemm(call, st::plan_gemm(call.w, call.rows, c->sm_count), workspace, stream);
+    return st::launch_gemm(call, st::plan_gemm(call.w, call.rows, c->sm_count), workspace, c->programmatic_launch,
+                           stream);
 }
 
 // workspace declared by the caller: size, alignment, aliasing, then device provenance

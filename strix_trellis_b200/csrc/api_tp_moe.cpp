@@ -552,6 +552,14 @@ strix_status strix_b200_moe_plan_rows(strix_tp_moe_plan p, const float** each, c
     *row_valid = p->device_routed ? p->row_valid : nullptr;
     return STRIX_SUCCESS;
 }
+strix_status strix_b200_moe_plan_gate_up_rows(strix_tp_moe_plan p, const float** gate, const float** up) {
+    if (gate) *gate = nullptr;
+    if (up) *up = nullptr;
+    if (!p || !gate || !up) return STRIX_ERROR_INVALID_ARGUMENT;
+    *gate = p->g;
+    *up = p->u;
+    return STRIX_SUCCESS;
+}
 
 // Staged diagnostics of the reference's split3 schedule have no counterpart in this one.
 strix_status strix_tp_moe_plan_down_core(strix_tp_moe_plan) { return STRIX_ERROR_NOT_IMPLEMENTED; }

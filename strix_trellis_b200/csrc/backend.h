@@ -50,6 +50,12 @@ struct LinearCall {
 // shared memory is a function attribute of ONE device).  Runs when a context is created, with
 // the context's device current; launches never set attributes.
 cudaError_t configure_device();
+int device_sm_count();
+// Grid of a grid-stride streaming kernel that wants `ctas` CTAs: at most `deep` per SM.
+inline int streaming_grid(long long ctas, int deep = 8) {
+    const long long cap = (long long)device_sm_count() * deep;
+    return (int)(ctas < cap ? (ctas < 1 ? 1 : ctas) : cap);
+}
 
 constexpr size_t kAlign = 256;
 inline size_t align_up(size_t v, size_t a = kAlign) { return (v + a - 1) / a * a; }
@@ -110,6 +116,6 @@ struct GemmPlan {
 };
 GemmPlan plan_gemm(const DeviceWeights& w, int rows, int sm_count);
 cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* workspace,
-                        cudaStream_t stream);
+                        bool programmatic_launch, cudaStream_t stream);
 
 }  // namespace st

@@ -1,6 +1,6 @@
 // Row counts above 8 that do not reach the tensor-core prefill kernel's minimum tile
-// (and every shape until that kernel is selected) run as 8-row chunks of the fused
-// GEMV, the same decomposition the reference uses for its vector route
+// run as 8-row chunks of the fused GEMV, the same decomposition the reference uses for
+// its vector route
 // (src/backend.hip:141-146).  Same arithmetic per row as strix_gemv.
 #include "backend.h"
 
@@ -19,7 +19,7 @@ GemmPlan plan_gemm_chunked(const DeviceWeights& w, int rows, int sm_count) {
     return plan;
 }
 
-cudaError_t launch_gemm_chunked(const LinearCall& call, int sm_count, void* workspace,
+cudaError_t launch_gemm_chunked(const LinearCall& call, int sm_count, void* workspace, bool programmatic_launch,
                                 cudaStream_t stream) {
     // Chunks of 8 rows use the 8-row plan; a shorter tail uses its own plan, whose
     // scratch requirement is never larger.
@@ -37,7 +37,7 @@ cudaError_t launch_gemm_chunked(const LinearCall& call, int sm_count, void* work
             if (e != cudaSuccess) return e;
             zeroed = true;
         }
-        const cudaError_t e = launch_gemv(part, g, workspace, true, stream);
+        const cudaError_t e = launch_gemv(part, g, workspace, programmatic_launch, stream);
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;

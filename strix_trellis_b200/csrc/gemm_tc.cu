@@ -375,33 +375,18 @@ __global__ void splitk_finish_kernel(const float* __restrict__ partials, int spl
 }
 
 // ---- host side ---------------------------------------------------------------------------------
-static bool tc_enabled() {
-    static const bool on = [] {
-        const char* e = getenv("STRIX_B200_GEMM");
-        return !(e && e[0] == 'c');  // "chunked" forces the 8-row GEMV route (measurement switch)
-    }();
-    return on;
-}
-
 GemmPlan plan_gemm_chunked(const DeviceWeights& w, int rows, int sm_count);
-cudaError_t launch_gemm_chunked(const LinearCall& call, int sm_count, void* workspace, cudaStream_t stream);
+cudaError_t launch_gemm_chunked(const LinearCall& call, int sm_count, void* workspace, bool programmatic_launch,
+                                cudaStream_t stream);
 
 // gemm_tc_pair.cu: two CTAs per 512 x 256 tile
 int gemm_pair_rows_padded(int rows);
 cudaError_t launch_gemm_pair(const LinearCall& call, const unsigned char* a_tiles, int sm_count, cudaStream_t stream);
 
-static bool pair_enabled() {
-    static const bool on = [] {
-        const char* e = getenv("STRIX_B200_GEMM");
-        return !(e && e[0] == 's');  // "single" keeps every row count on the one-CTA kernel (measurement switch)
-    }();
-    return on;
-}
-
 GemmPlan plan_gemm(const DeviceWeights& w, int rows, int sm_count) {
-    if (!tc_enabled() || rows < 64) return plan_gemm_chunked(w, rows, sm_count);
+    if (rows < 64) return plan_gemm_chunked(w, rows, sm_count);
     GemmPlan plan{};
-    const bool pair = rows > kBM * kMT && pair_enabled() && sm_count >= 2;
+    const bool pair = rows > kBM * kMT && sm_count >= 2;
     const int rows_padded = pair ? gemm_pair_rows_padded(rows) : (rows + kBM * kMT - 1) / (kBM * kMT) * (kBM * kMT);
     plan.act_bytes = (size_t)rows_padded * w.inputs * 2;
     plan.workspace_bytes = align_up(plan.act_bytes);
@@ -479,8 +464,10 @@ static cudaError_t launch_tc_bits(const GemmArgs& a, int grid, cudaStream_t s) {
     }
 }
 
-cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* workspace, cudaStream_t stream) {
-    if (!plan.tensor_core) return launch_gemm_chunked(call, plan.sm_count, workspace, stream);
+cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* workspace, bool programmatic_launch,
+                        cudaStream_t stream) {
+    // Only the 8-row chunks launch programmatically; the tensor-core kernels are ordinary launches.
+    if (!plan.tensor_core) return launch_gemm_chunked(call, plan.sm_count, workspace, programmatic_launch, stream);
     if (!workspace) return cudaErrorInvalidValue;
     const bool pair = plan.tile_m == 2 * kBM * kMT;
     const int m_pairs = (call.rows + kBM * kMT - 1) / (kBM * kMT);
@@ -488,7 +475,7 @@ cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* work
     {
         const long long groups = (long long)rows_padded * (call.w.inputs / 128);
         const long long want = (groups + 7) / 8;
-        const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+        const int grid = streaming_grid(want);
         input_tiles_kernel<<<grid, 256, 0, stream>>>(call.x, call.x_dtype, call.x_stride, call.w.suh, call.w.inputs, call.rows,
                                                      rows_padded, static_cast<unsigned char*>(workspace));
         const cudaError_t e = cudaGetLastError();
@@ -515,7 +502,7 @@ cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* work
     if (e != cudaSuccess || plan.k_splits == 1) return e;
     const long long items = (long long)call.rows * (call.w.outputs / 128);
     const long long want = (items + 7) / 8;
-    splitk_finish_kernel<<<(int)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(
+    splitk_finish_kernel<<<streaming_grid(want), 256, 0, stream>>>(
         args.partials, plan.k_splits, (size_t)rows_padded * call.w.outputs, call.rows, call.w.outputs, call.w.svh,
         call.w.bias, call.alpha, call.beta, call.y, call.y_dtype, call.y_stride);
     return cudaGetLastError();

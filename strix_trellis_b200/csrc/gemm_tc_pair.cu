@@ -3,27 +3,16 @@
 // of it as two 128 x 256 f32 accumulators (all 512 columns of its tensor memory), streams its
 // own two activation tiles per K step and DECODES ONLY ITS OWN 128 COLUMNS of the weight
 // stage -- the MMA reads the other 128 from the partner's shared memory.  Against the
-// single-CTA kernel (gemm_tc.cu) every decoded weight now feeds twice as many rows, which
-// halves the decode work per flop, the limit of that kernel.  Measured (K4, 4096 -> 12288):
-// 251 us against 306 us at 2048 rows, 962 us against 1069 us at 8192 rows.
-//
-// A variant with ONE accumulator per CTA (256-row pair tile), which leaves half of tensor memory
-// free so that the epilogue of a tile overlaps the next tile's main loop, measured slower
-// (1337 us against 1007 us at 8192 rows): each decoded weight then feeds 256 rows instead of
-// 512 and the decoders, not the epilogue, set the pace again.
-//
-// Eight epilogue warps (two per tensor-memory lane quarter, one per 128-column block) with a
-// three-stage ring measured 962 us at 8192 rows against 1007 us for four epilogue warps and
-// four stages; eight-row staging areas that would pay for a fourth stage measured 1015 us.
+// single-CTA kernel (gemm_tc.cu) every decoded weight feeds twice as many rows, which halves
+// the decode work per flop.
 //
 // Per CTA: warp 0 activation producer (bulk copies), warp 1 MMA issuer (leader CTA) or relay
 // (partner CTA: ONE remote arrival per stage once its activation tiles have landed and its
-// decoders are done -- sixteen remote arrivals per stage, one per decoder warp, measured
-// 20 % slower than the single-CTA kernel), warps 2-9 epilogue of the
-// CTA's own accumulators, warps 10-25 decoders (column tile = d % 8, K half = d / 8).
-// Barriers another CTA arrives on are waited with cluster scope; a tcgen05.commit arrives on
-// both CTAs' barriers at once.  Every wait is bounded and reports into the status word; both
-// CTAs meet at a cluster barrier before tensor memory is returned.
+// decoders are done), warps 2-9 epilogue of the CTA's own accumulators (two per tensor-memory
+// lane quarter, one per 128-column block), warps 10-25 decoders (column tile = d % 8,
+// K half = d / 8).  Barriers another CTA arrives on are waited with cluster scope; a
+// tcgen05.commit arrives on both CTAs' barriers at once.  Every wait is bounded and reports
+// into the status word; both CTAs meet at a cluster barrier before tensor memory is returned.
 #include "backend.h"
 #include "hadamard.cuh"
 #include "sync_primitives.cuh"

@@ -282,7 +282,7 @@ cudaError_t launch_swiglu(const float* gate, const float* up, float* hidden, int
     const long long count = (long long)rows * width;
     if (count <= 0) return cudaSuccess;
     const long long want = (count + 255) / 256;
-    swiglu_kernel<<<(int)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(gate, up, hidden, count, width, out_stride);
+    swiglu_kernel<<<streaming_grid(want), 256, 0, stream>>>(gate, up, hidden, count, width, out_stride);
     return cudaGetLastError();
 }
 
@@ -398,7 +398,7 @@ cudaError_t launch_moe_combine(const float* each, const float* scores, const int
     const long long total = (long long)tokens * outputs;
     if (total <= 0) return cudaSuccess;
     const long long want = (total + 255) / 256;
-    moe_combine_kernel<<<(int)(want < 148 * 8 ? want : 148 * 8), 256, 0, stream>>>(
+    moe_combine_kernel<<<streaming_grid(want), 256, 0, stream>>>(
         each, scores, row_valid, tokens, top_k, outputs, y, y_stride, alpha, beta, route_ids, first_expert, bank_count);
     return cudaGetLastError();
 }

@@ -31,7 +31,7 @@ cudaError_t launch_regroup(const uint32_t* src, uint32_t* dst, int inputs, int o
     const long long total = (long long)ktiles * ntiles * words;
     const int block = 256;
     const long long want = (total + block - 1) / block;
-    const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
+    const int grid = streaming_grid(want, 16);
     regroup_kernel<<<grid, block, 0, stream>>>(src, dst, ktiles, ntiles, words);
     return cudaGetLastError();
 }
@@ -90,7 +90,7 @@ static cudaError_t dequantize_bits(const DeviceWeights& w, uint16_t* q, int grid
 cudaError_t launch_dequantize(const DeviceWeights& w, uint16_t* q, cudaStream_t stream) {
     const long long tiles = (long long)(w.inputs / 16) * (w.outputs / 16);
     const long long want = (tiles + 7) / 8;
-    const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+    const int grid = streaming_grid(want);
     switch (w.codebook) {
     case CB_3INST: return dequantize_bits<CB_3INST>(w, q, grid, stream);
     case CB_MCG: return dequantize_bits<CB_MCG>(w, q, grid, stream);
@@ -132,7 +132,7 @@ cudaError_t launch_input_stages(const DeviceWeights& w, const float* x, long lon
                                 cudaStream_t stream) {
     const long long groups = (long long)rows * (w.inputs / 128);
     const long long want = (groups + 7) / 8;
-    const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+    const int grid = streaming_grid(want);
     input_stages_kernel<<<grid, 256, 0, stream>>>(x, x_stride, w.suh, w.inputs, rows, scaled16, had32,
                                                   core16);
     return cudaGetLastError();
@@ -168,7 +168,7 @@ cudaError_t launch_output_stages(const DeviceWeights& w, const float* core, int 
                                  cudaStream_t stream) {
     const long long groups = (long long)rows * (w.outputs / 128);
     const long long want = (groups + 7) / 8;
-    const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+    const int grid = streaming_grid(want);
     output_stages_kernel<<<grid, 256, 0, stream>>>(core, splits, rows, w.svh, w.bias, w.outputs, y,
                                                    y_stride, alpha, beta);
     return cudaGetLastError();

@@ -50,10 +50,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
     return false;
 }
 // Cluster-scope variants for barriers that another CTA of the cluster arrives on.
-#ifndef ST_CLUSTER_WAIT_HINT
-#define ST_CLUSTER_WAIT_HINT 100
-#endif
-constexpr uint32_t kClusterWaitHintNs = ST_CLUSTER_WAIT_HINT;
+constexpr uint32_t kClusterWaitHintNs = 100;  // suspend-time hint of one try_wait
 __device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(

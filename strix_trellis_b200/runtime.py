@@ -349,6 +349,16 @@ class MoePlan:
         return self.workspace[: self.tokens * self.top_k * self.inter * 4].view(torch.float32).view(
             self.tokens, self.top_k, self.inter)
 
+    def gate_up_rows(self):
+        """The gate and up projection rows of the last gate_up(), [tokens, top_k, intermediate]."""
+        from .peer import _Raw
+        g, u = N.vp(), N.vp()
+        N.check(self.lib.strix_b200_moe_plan_gate_up_rows(self.handle, C.byref(g), C.byref(u)),
+                "strix_b200_moe_plan_gate_up_rows")
+        nbytes = self.tokens * self.top_k * self.inter * 4
+        return tuple(torch.as_tensor(_Raw(p.value, nbytes), device="cuda").view(torch.float32).view(
+            self.tokens, self.top_k, self.inter) for p in (g, u))
+
     def close(self):
         if self.handle:
             N.check(self.lib.strix_tp_moe_plan_destroy(self.handle), "strix_tp_moe_plan_destroy")

@@ -144,7 +144,7 @@ GemmPlan plan_gemm(const DeviceWeights& w, int rows, int) {
     p.workspace_bytes = p.act_bytes;
     return p;
 }
-cudaError_t launch_gemm(const LinearCall& call, const GemmPlan&, void* workspace, cudaStream_t stream) {
+cudaError_t launch_gemm(const LinearCall& call, const GemmPlan&, void* workspace, bool, cudaStream_t stream) {
     record().last = call; record().last_workspace = workspace; record().last_stream = stream; record().last_was_gemm = true;
     return mock::launched();
 }

@@ -159,6 +159,72 @@ def test_moe_full_expert_size(ctx):
             w.close()
 
 
+def test_moe_full_expert_size_stage_by_stage(ctx):
+    """The same block taken apart, so that every stage meets the gate of what it is: (1) the gate
+    and up rows are single projections of x -- single-projection gates; (2) the hidden rows are
+    SwiGLU of the DEVICE's gate and up rows -- float32 arithmetic of a few roundings around one
+    exp, held to 16 ulp of the exactly evaluated product; (3) down and combine of the ORACLE's hidden rows -- a
+    score-weighted sum of single projections, single-projection gates again.  Only the chained
+    block needs the wider NRMSE bound, and this test shows that the width comes from the
+    binary16 rounding between stages 2 and 3 and from nothing else."""
+    from strix_trellis_b200.runtime import MoePlan
+    model, inter, n_exp, tokens, top_k = 4096, 2048, 16, 8, 8
+    layers = make_experts(n_exp, model, inter, 7000, bits_of=lambda e, k: 2)
+    ws = [tuple(ctx.prepare(l[k]) for k in ("gate", "up", "down")) for l in layers]
+    x = synthetic.make_activations(tokens, model, seed=7001)
+    ids, scores = synthetic.make_routes(tokens, n_exp, top_k, seed=7002)
+
+    def lin(v, w):
+        return c_oracle.linear(w.trellis, w.suh, w.svh, w.bias, w.bits, 2, v)
+
+    g_ref = np.zeros((tokens, top_k, inter), np.float32)
+    u_ref = np.zeros_like(g_ref)
+    for t in range(tokens):
+        for s_ in range(top_k):
+            g_ref[t, s_] = lin(x[t:t + 1], layers[ids[t, s_]]["gate"])[0]
+            u_ref[t, s_] = lin(x[t:t + 1], layers[ids[t, s_]]["up"])[0]
+    h_ref = ref.swiglu(g_ref, u_ref)
+
+    y = torch.zeros((tokens, model), device="cuda")
+    plan = MoePlan(ctx, ws, dev(x), y, dev(ids.astype(np.uint32).view(np.int32)).view(torch.int32), dev(scores),
+                   device_routed=True)
+    plan.gate_up()
+    torch.cuda.synchronize()
+    g_dev, u_dev = (host(t) for t in plan.gate_up_rows())
+    gate(g_dev.reshape(tokens * top_k, inter), g_ref.reshape(tokens * top_k, inter), "gate rows")
+    gate(u_dev.reshape(tokens * top_k, inter), u_ref.reshape(tokens * top_k, inter), "up rows")
+    # (2) SwiGLU of the device's own rows, against the expression evaluated in float64 (NumPy's
+    # float32 exp and the device's expf are each a couple of ulp off the true value, so neither
+    # is the yardstick for the other)
+    h_dev = host(plan.hidden())
+    g64, u64 = g_dev.astype(np.float64), u_dev.astype(np.float64)
+    h_true = g64 / (1.0 + np.exp(-g64)) * u64
+    ulp = np.spacing(np.abs(h_true).astype(np.float32)).astype(np.float64)
+    h_f32 = ref.swiglu(g_dev, u_dev).astype(np.float64)  # the same float32 steps in NumPy
+    # where exp(-|g|) leaves the normal float32 range the float32 steps themselves lose bits:
+    # there the float32 restatement is the yardstick, elsewhere the exact value
+    normal = np.abs(g64) < 80.0
+    off_true = np.abs(h_dev.astype(np.float64) - h_true) / ulp
+    off_f32 = np.abs(h_dev.astype(np.float64) - h_f32) / ulp
+    assert off_true[normal].max() <= 16.0, float(off_true[normal].max())
+    assert (~normal).sum() == 0 or off_f32[~normal].max() <= 16.0, float(off_f32[~normal].max())
+    # (3) down + combine of the oracle's hidden rows
+    plan.hidden().copy_(dev(h_ref))
+    plan.down()
+    torch.cuda.synchronize()
+    want = np.zeros((tokens, model), np.float32)
+    for t in range(tokens):
+        for s_ in range(top_k):
+            if scores[t, s_] != 0:
+                want[t] = want[t] + scores[t, s_] * lin(h_ref[t, s_:s_ + 1], layers[ids[t, s_]]["down"])[0]
+    assert ctx.device_status() == 0
+    gate(host(y), want, "down and combine of the oracle's hidden rows")
+    plan.close()
+    for t in ws:
+        for w in t:
+            w.close()
+
+
 def test_standalone_combine_is_the_plan_combine(ctx):
     """strix_b200_moe_combine: ascending slot order from +0 with separately rounded products, a
     zero score skips its slot (even over a NaN row), alpha/beta as in the plans -- bit for bit
