@@ -431,7 +431,12 @@ def ep_case(torch, dist, ctx, stream, rank, world, tokens_list=(1, 8, 64), exper
                 for sc in sets[0][1][token]:  # ascending slot order from +0; every expert holds the same layers
                     if sc != 0.0:
                         want = want + np.float32(sc) * down
-                m = _gates(got[j], want, f"expert-parallel block, token {token}, {t} tokens, rank {rank}", 2.5e-4)
+                # One token row whose eight slots hold the same expert layers: the slots' errors
+                # (binary16 roundings of the hidden row that flip with the accumulation order) are
+                # fully correlated, so a row's NRMSE scatters around the 8-token block figure the
+                # tests hold to 2.5e-4; rows are held to twice that.  tests/test_gpu_moe.py takes
+                # the block apart stage by stage at single-projection gates.
+                m = _gates(got[j], want, f"expert-parallel block, token {token}, {t} tokens, rank {rank}", 5e-4)
                 worst = [max(a, b) for a, b in zip(worst, m)]
             if world > 1:
                 dist.barrier()  # the CPU check takes seconds on some ranks and nothing on others
