@@ -224,8 +224,20 @@ __global__ void __launch_bounds__(kThreads) peer_gather_kernel(const GatherArgs 
             const long long words = (long long)a.total_rows * a.total_cols[m];
             const uint32_t* landed = reinterpret_cast<const uint32_t*>(a.view.arena[t.rank]) + a.region[m] / 4 + (long long)t.parity() * words;
             if (a.total_cols[m] % 4 == 0) {
-                for (long long i = lane0; i < words / 4; i += step)
-                    reinterpret_cast<uint4*>(out)[i] = ld_sys_v4(reinterpret_cast<const uint4*>(landed) + i);
+                // four loads in flight per thread: the copy is latency, not bandwidth
+                const uint4* from = reinterpret_cast<const uint4*>(landed);
+                uint4* to = reinterpret_cast<uint4*>(out);
+                const long long quads = words / 4;
+                long long i = lane0;
+                for (; i + 3 * step < quads; i += 4 * step) {
+                    const uint4 v0 = ld_sys_v4(from + i), v1 = ld_sys_v4(from + i + step);
+                    const uint4 v2 = ld_sys_v4(from + i + 2 * step), v3 = ld_sys_v4(from + i + 3 * step);
+                    to[i] = v0;
+                    to[i + step] = v1;
+                    to[i + 2 * step] = v2;
+                    to[i + 3 * step] = v3;
+                }
+                for (; i < quads; i += step) to[i] = ld_sys_v4(from + i);
             } else {
                 for (long long i = lane0; i < words; i += step) out[i] = ld_sys_u32(landed + i);
             }

@@ -163,7 +163,7 @@ def test_moe_full_expert_size_stage_by_stage(ctx):
     """The same block taken apart, so that every stage meets the gate of what it is: (1) the gate
     and up rows are single projections of x -- single-projection gates; (2) the hidden rows are
     SwiGLU of the DEVICE's gate and up rows -- float32 arithmetic of a few roundings around one
-    exp, held to 16 ulp of the exactly evaluated product; (3) down and combine of the ORACLE's hidden rows -- a
+    exp, held to 16 ulp of the exactly evaluated product (1e-9 absolute near zero); (3) down and combine of the ORACLE's hidden rows -- a
     score-weighted sum of single projections, single-projection gates again.  Only the chained
     block needs the wider NRMSE bound, and this test shows that the width comes from the
     binary16 rounding between stages 2 and 3 and from nothing else."""
@@ -200,14 +200,12 @@ def test_moe_full_expert_size_stage_by_stage(ctx):
     g64, u64 = g_dev.astype(np.float64), u_dev.astype(np.float64)
     h_true = g64 / (1.0 + np.exp(-g64)) * u64
     ulp = np.spacing(np.abs(h_true).astype(np.float32)).astype(np.float64)
-    h_f32 = ref.swiglu(g_dev, u_dev).astype(np.float64)  # the same float32 steps in NumPy
-    # where exp(-|g|) leaves the normal float32 range the float32 steps themselves lose bits:
-    # there the float32 restatement is the yardstick, elsewhere the exact value
-    normal = np.abs(g64) < 80.0
-    off_true = np.abs(h_dev.astype(np.float64) - h_true) / ulp
-    off_f32 = np.abs(h_dev.astype(np.float64) - h_f32) / ulp
-    assert off_true[normal].max() <= 16.0, float(off_true[normal].max())
-    assert (~normal).sum() == 0 or off_f32[~normal].max() <= 16.0, float(off_f32[~normal].max())
+    # 16 ulp, or 1e-9 absolute where exp(-|g|) leaves the normal float32 range and the float32
+    # steps lose bits: a sixtieth of the smallest binary16 subnormal, i.e. nothing the binary16
+    # rounding in front of the down projection can tell from zero
+    bound = np.maximum(16.0 * ulp, 1e-9)
+    assert (np.abs(h_dev.astype(np.float64) - h_true) <= bound).all()
+    assert (np.abs(ref.swiglu(g_dev, u_dev).astype(np.float64) - h_true) <= bound).all()  # the oracle's own steps
     # (3) down + combine of the oracle's hidden rows
     plan.hidden().copy_(dev(h_ref))
     plan.down()
