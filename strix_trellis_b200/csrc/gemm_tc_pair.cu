@@ -68,7 +68,9 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
         for (int i = 0; i < kStagesP; ++i) {
             mbar_init(full_a + 8 * i, 1);
             mbar_init(full_b + 8 * i, kDecodeWarps);      // this CTA's decoders
-            mbar_init(peer_a + 8 * i, 1);                  // leader's: the partner's whole stage is ready
+            // leader's: ONE barrier per stage for everything its MMA warp waits for -- its own activation
+            // copies (one arrival + bytes), its sixteen decoders and the partner's relay
+            mbar_init(peer_a + 8 * i, 1 + kDecodeWarps + 1);
             mbar_init(empty + 8 * i, 1);
         }
         mbar_init(tmem_full, 1);
@@ -76,6 +78,9 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
         mbar_fence_init();
         s_abort = 0;
     }
+    // where this CTA's activation copies and decoders report: the leader's merged barrier, or the
+    // two barriers the partner's relay waits for
+    const uint32_t a_bar = rank == 0 ? peer_a : full_a, b_bar = rank == 0 ? peer_a : full_b;
     if (warp == 1) tmem_alloc_pair(smem_u32(&s_tmem_base), kTmemCols);
     tc_fence_before_sync();
     cluster_sync_all();  // barriers initialised and tensor memory allocated in BOTH CTAs
@@ -97,16 +102,16 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
                         break;
                     }
                     unsigned char* dst = ring + (size_t)st * kStageBytesP;
-                    mbar_expect_tx(full_a + 8 * st, kMT * kTileBytes);
+                    mbar_expect_tx(a_bar + 8 * st, kMT * kTileBytes);
 #pragma unroll
                     for (int mt = 0; mt < kMT; ++mt)
                         bulk_load(smem_u32(dst + mt * kTileBytes),
                                   args.a_tiles + ((size_t)(mq * 4 + (int)rank * 2 + mt) * kt64 + ks) * kTileBytes,
-                                  kTileBytes, full_a + 8 * st);
+                                  kTileBytes, a_bar + 8 * st);
                 }
             }
             for (int i = (it > kStagesP ? it - kStagesP : 0); i < it; ++i)  // nothing still landing at exit
-                mbar_wait(full_a + 8 * (i % kStagesP), (uint32_t)(i / kStagesP) & 1, c.status, kTimeoutDrain);
+                mbar_wait(a_bar + 8 * (i % kStagesP), (uint32_t)(i / kStagesP) & 1, c.status, kTimeoutDrain);
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
@@ -122,9 +127,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
                 for (int ks = 0; ks < kt64 && !s_abort; ++ks, ++it) {
                     const int st = it % kStagesP;
                     const uint32_t par = (uint32_t)(it / kStagesP) & 1;
-                    if (!mbar_wait(full_a + 8 * st, par, c.status, kTimeoutTensorPipe) ||
-                        !mbar_wait_cluster(peer_a + 8 * st, par, c.status, kTimeoutTensorPipe) ||
-                        !mbar_wait(full_b + 8 * st, par, c.status, kTimeoutTensorPipe)) {
+                    if (!mbar_wait_cluster(peer_a + 8 * st, par, c.status, kTimeoutTensorPipe)) {
                         s_abort = 1;
                         break;
                     }
@@ -280,7 +283,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(full_b + 8 * st);  // local: the relay (partner) or the MMA warp (leader) waits on it
+            if (lane == 0) mbar_arrive(b_bar + 8 * st);  // local: the relay (partner) or the MMA warp (leader) waits on it
 #pragma unroll
             for (int k2 = 0; k2 < 2; ++k2)
 #pragma unroll
