@@ -99,14 +99,14 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                                                  (size_t)kEpiWarps * kStagingBytes);
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
-    const uint32_t full_a = smem_u32(bars), full_b = smem_u32(bars + kStagesTc),
-                   empty = smem_u32(bars + 2 * kStagesTc), tmem_full = smem_u32(bars + 3 * kStagesTc),
-                   tmem_empty = smem_u32(bars + 3 * kStagesTc + 1);
+    const uint32_t full = smem_u32(bars), empty = smem_u32(bars + kStagesTc), tmem_full = smem_u32(bars + 2 * kStagesTc),
+                   tmem_empty = smem_u32(bars + 2 * kStagesTc + 1);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStagesTc; ++i) {
-            mbar_init(full_a + 8 * i, 1);
-            mbar_init(full_b + 8 * i, kDecodeWarps);
+            // ONE barrier per stage for everything the MMA warp waits for: the activation copies (one
+            // arrival + bytes) and the sixteen decoders
+            mbar_init(full + 8 * i, 1 + kDecodeWarps);
             mbar_init(empty + 8 * i, 1);
         }
         mbar_init(tmem_full, 1);
@@ -135,17 +135,17 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                         break;
                     }
                     unsigned char* dst = ring + (size_t)st * kStageBytesTc;
-                    mbar_expect_tx(full_a + 8 * st, kMT * kTileBytes);
+                    mbar_expect_tx(full + 8 * st, kMT * kTileBytes);
 #pragma unroll
                     for (int mt = 0; mt < kMT; ++mt)
                         bulk_load(smem_u32(dst + mt * kTileBytes),
                                   args.a_tiles + ((size_t)(mp * kMT + mt) * kt64 + ks) * kTileBytes, kTileBytes,
-                                  full_a + 8 * st);
+                                  full + 8 * st);
                 }
             }
             // Never leave with a copy still landing in this CTA's shared memory.
             for (int i = (it > kStagesTc ? it - kStagesTc : 0); i < it; ++i)
-                mbar_wait(full_a + 8 * (i % kStagesTc), (uint32_t)(i / kStagesTc) & 1, c.status, kTimeoutDrain);
+                mbar_wait(full + 8 * (i % kStagesTc), (uint32_t)(i / kStagesTc) & 1, c.status, kTimeoutDrain);
         }
     } else if (warp == 1) {
         // ---- MMA issuer ---------------------------------------------------------------
@@ -163,8 +163,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                 for (int ks = kb, ke = k_end_of(t); ks < ke && !s_abort; ++ks, ++it) {
                     const int st = it % kStagesTc;
                     const uint32_t par = (uint32_t)(it / kStagesTc) & 1;
-                    if (!mbar_wait(full_a + 8 * st, par, c.status, kTimeoutTensorPipe) ||
-                        !mbar_wait(full_b + 8 * st, par, c.status, kTimeoutTensorPipe)) {
+                    if (!mbar_wait(full + 8 * st, par, c.status, kTimeoutTensorPipe)) {
                         s_abort = 1;
                         break;
                     }
@@ -328,7 +327,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(full_b + 8 * st);
+            if (lane == 0) mbar_arrive(full + 8 * st);
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4)
 #pragma unroll
