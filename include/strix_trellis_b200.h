@@ -164,6 +164,10 @@ strix_status strix_b200_peer_group_create(strix_context context, void *const *lo
                                           uint64_t arena_bytes, const unsigned char *handles,
                                           uint32_t world, strix_b200_peer_group *out);
 strix_status strix_b200_peer_group_destroy(strix_b200_peer_group group);
+/* How many times a wait for a peer polls before it gives up, sets bit 5 of the device status
+ * word and lets its kernel return (default 2^23, several seconds).  After a wait has run out the
+ * group's exchange numbering no longer matches its peers': destroy it and make a new one. */
+strix_status strix_b200_peer_group_set_wait_polls(strix_b200_peer_group group, uint32_t polls);
 
 /* rows[i] (count floats, count even, 8-byte aligned) of every rank is replaced by the sum over
  * ranks, added in ascending rank order from +0: identical bits on every rank.  Meant for the

@@ -52,7 +52,9 @@ struct PeerView {
     unsigned char* arena[kRanks];  // every rank's arena as mapped into this process
     int world, first_rank;
     unsigned int* status;
+    uint32_t wait_polls;  // polls of one wait before it gives up (strix_b200_peer_group_set_wait_polls)
 };
+constexpr uint32_t kDefaultWaitPolls = 1u << 23;  // several seconds: ranks of one job may be a second apart on the host
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
@@ -110,7 +112,7 @@ __device__ __forceinline__ bool exchange_wait(const PeerView& v, const Turn& t) 
     if ((int)threadIdx.x < v.world) {
         const uint32_t* flag = &t.mine->flags[t.parity()][threadIdx.x][blockIdx.x];
         bool seen = false;
-        for (uint32_t tries = 0; tries < (1u << 23) && !seen; ++tries) seen = ld_acquire_sys(flag) == t.epoch;
+        for (uint32_t tries = 0; tries < v.wait_polls && !seen; ++tries) seen = ld_acquire_sys(flag) == t.epoch;
         if (!seen) {
             if (v.status) atomicOr(v.status, kTimeoutPeer);
             s_late = 1;
@@ -159,7 +161,7 @@ __global__ void __launch_bounds__(kThreads) peer_sum_kernel(const ReduceArgs a) 
         for (int r = 0; r < a.view.world && !late; ++r) {
             uint4 part = ld_sys_v4(slots + (long long)r * a.count2 + i);
             for (uint32_t tries = 0; (part.y != t.epoch || part.w != t.epoch) && !late; ++tries) {
-                if (tries >= (1u << 23)) late = true;  // bounded: several seconds
+                if (tries >= a.view.wait_polls) late = true;  // bounded
                 else part = ld_sys_v4(slots + (long long)r * a.count2 + i);
             }
             s0 = __fadd_rn(s0, __uint_as_float(part.x));
@@ -356,6 +358,7 @@ strix_status strix_b200_peer_group_create(strix_context c, void* const* local_ar
     g->view.world = (int)world;
     g->view.first_rank = (int)first_rank;
     g->view.status = c->status;
+    g->view.wait_polls = kDefaultWaitPolls;
     cudaError_t e = cudaSuccess;
     for (uint32_t r = 0; r < world && e == cudaSuccess; ++r) {
         if (r >= first_rank && r < first_rank + local_count) {
@@ -380,6 +383,12 @@ strix_status strix_b200_peer_group_create(strix_context c, void* const* local_ar
         return cuda_status(e);
     }
     *out = g;
+    return STRIX_SUCCESS;
+}
+
+strix_status strix_b200_peer_group_set_wait_polls(strix_b200_peer_group g, uint32_t polls) {
+    if (!g || polls == 0) return STRIX_ERROR_INVALID_ARGUMENT;
+    g->view.wait_polls = polls;
     return STRIX_SUCCESS;
 }
 

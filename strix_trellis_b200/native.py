@@ -226,6 +226,7 @@ PROTOTYPES = {
     "strix_b200_moe_plan_projections": (C.c_int, [vp]),
     "strix_b200_moe_plan_rows": (C.c_int, [vp, P(vp), P(vp)]),
     "strix_b200_moe_plan_gate_up_rows": (C.c_int, [vp, P(vp), P(vp)]),
+    "strix_b200_peer_group_set_wait_polls": (C.c_int, [vp, C.c_uint32]),
     "strix_b200_peer_arena_create": (C.c_int, [vp, u64, P(vp), C.c_char_p]),
     "strix_b200_peer_arena_destroy": (C.c_int, [vp, vp]),
     "strix_b200_peer_group_create": (C.c_int, [vp, P(vp), u32, u32, u64, C.c_char_p, u32, P(vp)]),

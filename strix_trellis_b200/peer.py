@@ -51,6 +51,11 @@ class PeerGroup:
             import torch.distributed as dist
             dist.barrier(group=group)  # nobody stores into an arena before everybody has mapped it
 
+    def set_wait_polls(self, polls):
+        """How long a wait for a peer polls before it reports bit 5 of the device status word."""
+        N.check(self.lib.strix_b200_peer_group_set_wait_polls(self.handle, int(polls)),
+                "strix_b200_peer_group_set_wait_polls")
+
     # -- regions --------------------------------------------------------------------------
     def reserve(self, payload_bytes):
         """Offset of a fresh region for an exchange whose payload is `payload_bytes`."""

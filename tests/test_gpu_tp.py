@@ -230,3 +230,51 @@ def test_two_ranks_over_peer_memory(tmp_path):
     assert np.isnan(got_ep[5]).all()               # the token with an id outside the id space
     gate(got_ep[:5], want_ep[:5], "expert-parallel block", MOE_REL, MOE_NRMSE)
     assert got_graph[:5].tobytes() == got_ep[:5].tobytes() and np.isnan(got_graph[5]).all()
+
+
+def _absent_peer_rank(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    from strix_trellis_b200.peer import PeerGroup
+    from strix_trellis_b200.runtime import Context
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    ctx = Context(rank)
+    count = 2048
+    group = PeerGroup(ctx, 1 << 20, rank=rank, world=world)
+    region = group.reserve(world * count * 8)
+    group.set_wait_polls(1 << 16)  # a tenth of a second instead of several
+    rows = torch.full((count,), float(rank + 1), device="cuda")
+    late = 0
+    if rank == 0:  # rank 1 never joins this exchange: nothing sets the words rank 0 waits for
+        group.sum_rows([rows], region)
+        torch.cuda.synchronize()
+        late = ctx.device_status()
+    dist.barrier()  # rank 1 was idle meanwhile: it has nothing in flight
+    untouched = bool((rows == float(rank + 1)).all().item())
+    group.close()
+    # the context is still usable: a fresh group's exchange completes on both ranks
+    again = PeerGroup(ctx, 1 << 20, rank=rank, world=world)
+    region = again.reserve(world * count * 8)
+    again.sum_rows([rows], region)
+    torch.cuda.synchronize()
+    np.savez(out + f".{rank}.npz", late=late, untouched=untouched, total=rows.cpu().numpy(), after=ctx.device_status())
+    again.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_a_peer_that_never_arrives_is_reported_and_the_context_survives(tmp_path):
+    """Failure detection without a fault: one rank simply does not take part in an exchange.  The
+    other rank's wait runs out after its (shortened) limit, bit 5 of its device status word says
+    so, its rows are left as they were, and after the group has been replaced both ranks
+    exchange normally again."""
+    import torch.multiprocessing as mp
+    world, out = 2, str(tmp_path / "rank")
+    mp.spawn(_absent_peer_rank, args=(world, _free_port(), out), nprocs=world, join=True)
+    r0, r1 = (np.load(out + f".{rank}.npz") for rank in range(world))
+    assert int(r0["late"]) == 32 and int(r1["late"]) == 0
+    assert bool(r0["untouched"]) and bool(r1["untouched"])
+    for r in (r0, r1):
+        assert int(r["after"]) == 0
+        assert (r["total"] == 3.0).all()
