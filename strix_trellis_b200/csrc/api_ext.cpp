@@ -149,7 +149,7 @@ strix_status strix_b200_moe_combine_rows(strix_context c, const float* rows, con
         return STRIX_ERROR_INVALID_ARGUMENT;
     }
     return cuda_status(st::launch_moe_combine(rows, scores, row_valid, (int)tokens, (int)top_k, (int)width, y,
-                                              (long long)y_stride, alpha, beta, cs));
+                                              (long long)y_stride, alpha, beta, c->programmatic_launch, cs));
 }
 
 strix_status strix_b200_moe_combine(strix_context c, const float* rows, const float* scores, uint32_t tokens,

@@ -244,12 +244,13 @@ strix_status enqueue_gate_up(strix_tp_moe_plan_impl* p) {
     cudaError_t e = cudaSuccess;
     if (p->device_routed)
         e = st::launch_moe_route(p->route_ids, p->scores, p->tokens, p->top_k, p->bank, p->bank_count, p->window, p->gu,
-                                 p->down, p->row_valid, p->stream);
+                                 p->down, p->row_valid, p->owner->programmatic_launch, p->stream);
     if (e == cudaSuccess)
         e = st::launch_grouped(p->gu, p->gu_count, p->model, p->inter, p->codebook, p->gu_plan, p->owner->status,
                                p->owner->programmatic_launch, p->stream);
     if (e == cudaSuccess)
-        e = st::launch_swiglu(p->g, p->u, p->hidden, p->tokens * p->top_k, p->inter, p->inter, p->stream);
+        e = st::launch_swiglu(p->g, p->u, p->hidden, p->tokens * p->top_k, p->inter, p->inter,
+                              p->owner->programmatic_launch, p->stream);
     return cuda_status(e);
 }
 
@@ -259,8 +260,8 @@ strix_status enqueue_down(strix_tp_moe_plan_impl* p, bool combine = true) {
     if (e == cudaSuccess && combine) {
         const bool partial = p->device_routed && p->window.experts_total != p->bank_count;  // other ranks own some slots
         e = st::launch_moe_combine(p->each, p->scores, p->device_routed ? p->row_valid : nullptr, p->tokens, p->top_k,
-                                   p->model, p->y, p->y_stride, p->alpha, p->beta, p->stream,
-                                   partial ? p->route_ids : nullptr, p->window.first_expert, p->bank_count);
+                                   p->model, p->y, p->y_stride, p->alpha, p->beta, p->owner->programmatic_launch,
+                                   p->stream, partial ? p->route_ids : nullptr, p->window.first_expert, p->bank_count);
     }
     return cuda_status(e);
 }
@@ -689,7 +690,9 @@ strix_status strix_tp_swiglu_plan_submit(strix_tp_swiglu_plan p) {
     if (s != STRIX_SUCCESS) return s;
     cudaError_t e = st::launch_grouped(p->problems, 2, p->inputs, p->inter, p->codebook, p->plan, p->owner->status,
                                        p->owner->programmatic_launch, p->stream);
-    if (e == cudaSuccess) e = st::launch_swiglu(p->g, p->u, p->hidden, p->rows, p->inter, p->hidden_stride, p->stream);
+    if (e == cudaSuccess)
+        e = st::launch_swiglu(p->g, p->u, p->hidden, p->rows, p->inter, p->hidden_stride, p->owner->programmatic_launch,
+                              p->stream);
     return cuda_status(e);
 }
 

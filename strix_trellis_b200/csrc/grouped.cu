@@ -267,6 +267,8 @@ cudaError_t launch_grouped(const GroupedProblem* problems, int problem_count, in
 // ---- SwiGLU and routed-expert combine --------------------------------------------------------
 __global__ void swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up,
                               float* __restrict__ hidden, long long count, int width, long long out_stride) {
+    pdl_wait_prior_grid();  // gate / up come from the launch before
+    pdl_launch_dependents();
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
          i += (long long)gridDim.x * blockDim.x) {
         const float g = gate[i];
@@ -277,13 +279,30 @@ __global__ void swiglu_kernel(const float* __restrict__ gate, const float* __res
     }
 }
 
+// A small kernel of a routed-expert submit: launched programmatically when the context allows
+// it, so that it is resident and waiting when the launch before it ends.
+template <class... Params, class... Args>
+static cudaError_t launch_small(void (*kernel)(Params...), int grid, int block, bool programmatic, cudaStream_t stream,
+                                Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 cudaError_t launch_swiglu(const float* gate, const float* up, float* hidden, int rows, int width,
-                          long long out_stride, cudaStream_t stream) {
+                          long long out_stride, bool programmatic, cudaStream_t stream) {
     const long long count = (long long)rows * width;
     if (count <= 0) return cudaSuccess;
     const long long want = (count + 255) / 256;
-    swiglu_kernel<<<streaming_grid(want), 256, 0, stream>>>(gate, up, hidden, count, width, out_stride);
-    return cudaGetLastError();
+    return launch_small(swiglu_kernel, streaming_grid(want), 256, programmatic, stream, gate, up, hidden, count, width,
+                        out_stride);
 }
 
 // Device-side routing, one CTA.  A row is valid when its ids are in range and distinct and
@@ -297,10 +316,12 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const unsigned int* __r
                                                          const MoeBankEntry* __restrict__ bank, int bank_count,
                                                          const MoeWindow window, GroupedProblem* gate_up,
                                                          GroupedProblem* down, int* row_valid) {
-    __shared__ int count[1024], first_problem[1024], cursor[1024], scan[1024];
+    __shared__ int count[1024], first_problem[1024], cursor[1024], warp_total[32];
     const int tid = threadIdx.x, routes = tokens * top_k;
     count[tid] = 0;
     cursor[tid] = 0;
+    pdl_wait_prior_grid();  // ids and scores may come from the launch before
+    pdl_launch_dependents();
     __syncthreads();
     for (int t = tid; t < tokens; t += 1024) {
         bool valid = true;
@@ -321,15 +342,27 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const unsigned int* __r
     __syncthreads();
     const int n = tid < bank_count ? count[tid] : 0;
     const int problems = (n + kGroupRows - 1) / kGroupRows;
-    scan[tid] = problems;
-    __syncthreads();
-    for (int off = 1; off < 1024; off <<= 1) {  // inclusive scan of problems per expert
-        const int add = tid >= off ? scan[tid - off] : 0;
-        __syncthreads();
-        scan[tid] += add;
-        __syncthreads();
+    // inclusive scan of problems per expert: within a warp by shuffles, then over the 32 warp totals
+    int incl = problems;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int up = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+        if ((tid & 31) >= off) incl += up;
     }
-    const int begin = scan[tid] - problems, total = scan[1023];
+    if ((tid & 31) == 31) warp_total[tid >> 5] = incl;
+    __syncthreads();
+    if (tid < 32) {
+        int w = warp_total[tid];
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int up = __shfl_up_sync(0xFFFFFFFFu, w, off);
+            if (tid >= off) w += up;
+        }
+        warp_total[tid] = w;
+    }
+    __syncthreads();
+    const int before = (tid >> 5) ? warp_total[(tid >> 5) - 1] : 0;
+    const int begin = before + incl - problems, total = warp_total[31];
     first_problem[tid] = begin;
     for (int k = 0; k < problems; ++k) {
         const int q = begin + k;
@@ -358,18 +391,19 @@ __global__ void __launch_bounds__(1024) moe_route_kernel(const unsigned int* __r
 
 cudaError_t launch_moe_route(const unsigned int* route_ids, const float* route_scores, int tokens, int top_k,
                              const MoeBankEntry* bank, int bank_count, MoeWindow window, GroupedProblem* gate_up,
-                             GroupedProblem* down, int* row_valid, cudaStream_t stream) {
+                             GroupedProblem* down, int* row_valid, bool programmatic, cudaStream_t stream) {
     if (bank_count > 1024 || window.first_expert < 0 || window.experts_total < window.first_expert + bank_count)
         return cudaErrorInvalidValue;
-    moe_route_kernel<<<1, 1024, 0, stream>>>(route_ids, route_scores, tokens, top_k, bank, bank_count, window, gate_up,
-                                             down, row_valid);
-    return cudaGetLastError();
+    return launch_small(moe_route_kernel, 1, 1024, programmatic, stream, route_ids, route_scores, tokens, top_k, bank,
+                        bank_count, window, gate_up, down, row_valid);
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ each, const float* __restrict__ scores,
                                    const int* __restrict__ row_valid, int tokens, int top_k, int outputs,
                                    float* y, long long y_stride, float alpha, float beta,
                                    const unsigned int* __restrict__ route_ids, int first_expert, int bank_count) {
+    pdl_wait_prior_grid();  // the routed rows come from the launch before
+    pdl_launch_dependents();
     const long long total = (long long)tokens * outputs;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -394,13 +428,13 @@ __global__ void moe_combine_kernel(const float* __restrict__ each, const float* 
 
 cudaError_t launch_moe_combine(const float* each, const float* scores, const int* row_valid, int tokens,
                                int top_k, int outputs, float* y, long long y_stride, float alpha, float beta,
-                               cudaStream_t stream, const unsigned int* route_ids, int first_expert, int bank_count) {
+                               bool programmatic, cudaStream_t stream, const unsigned int* route_ids, int first_expert,
+                               int bank_count) {
     const long long total = (long long)tokens * outputs;
     if (total <= 0) return cudaSuccess;
     const long long want = (total + 255) / 256;
-    moe_combine_kernel<<<streaming_grid(want), 256, 0, stream>>>(
-        each, scores, row_valid, tokens, top_k, outputs, y, y_stride, alpha, beta, route_ids, first_expert, bank_count);
-    return cudaGetLastError();
+    return launch_small(moe_combine_kernel, streaming_grid(want), 256, programmatic, stream, each, scores, row_valid, tokens,
+                        top_k, outputs, y, y_stride, alpha, beta, route_ids, first_expert, bank_count);
 }
 
 }  // namespace st

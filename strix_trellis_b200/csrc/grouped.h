@@ -40,7 +40,7 @@ cudaError_t launch_grouped(const GroupedProblem* problems, int problem_count, in
 // hidden[r][c] = SwiGLU(gate[r][c], up[r][c]); gate/up contiguous [rows][width], hidden rows
 // `out_stride` apart (src/tp_moe_activation.hpp:52-59).
 cudaError_t launch_swiglu(const float* gate, const float* up, float* hidden, int rows, int width,
-                          long long out_stride, cudaStream_t stream);
+                          long long out_stride, bool programmatic, cudaStream_t stream);
 
 // Device-side routing for a persistent expert bank: validates each token's route row and
 // groups the valid routes by expert into problem slots of up to kGroupRows rows each
@@ -53,7 +53,7 @@ struct MoeBankEntry { DeviceWeights gate, up, down; };
 struct MoeWindow { int first_expert, experts_total; };
 cudaError_t launch_moe_route(const unsigned int* route_ids, const float* route_scores, int tokens, int top_k,
                              const MoeBankEntry* bank, int bank_count, MoeWindow window, GroupedProblem* gate_up,
-                             GroupedProblem* down, int* row_valid, cudaStream_t stream);
+                             GroupedProblem* down, int* row_valid, bool programmatic, cudaStream_t stream);
 
 // Routed-expert combine: y[t] = alpha * sum_{s ascending, from +0} RN32(score[t,s]*each[t,s]) + beta*y[t];
 // a zero score skips its slot; a row flagged invalid becomes NaN (src/tp_moe.hip:112-164).
@@ -61,7 +61,7 @@ cudaError_t launch_moe_route(const unsigned int* route_ids, const float* route_s
 // result is this rank's contribution (the reference's per-rank semantics, include/strix_trellis.h:215-216).
 cudaError_t launch_moe_combine(const float* each, const float* scores, const int* row_valid, int tokens,
                                int top_k, int outputs, float* y, long long y_stride, float alpha, float beta,
-                               cudaStream_t stream, const unsigned int* route_ids = nullptr, int first_expert = 0,
-                               int bank_count = 0);
+                               bool programmatic, cudaStream_t stream, const unsigned int* route_ids = nullptr,
+                               int first_expert = 0, int bank_count = 0);
 
 }  // namespace st

@@ -156,7 +156,7 @@ GroupedPlan plan_grouped(int, int outputs, int, int, int) {
     return p;
 }
 cudaError_t launch_grouped(const GroupedProblem*, int, int, int, int, const GroupedPlan&, unsigned int*, bool, cudaStream_t) { return mock::launched(); }
-cudaError_t launch_swiglu(const float*, const float*, float*, int, int, long long, cudaStream_t) { return mock::launched(); }
-cudaError_t launch_moe_route(const unsigned int*, const float*, int, int, const MoeBankEntry*, int, MoeWindow, GroupedProblem*, GroupedProblem*, int*, cudaStream_t) { return mock::launched(); }
-cudaError_t launch_moe_combine(const float*, const float*, const int*, int, int, int, float*, long long, float, float, cudaStream_t, const unsigned int*, int, int) { return mock::launched(); }
+cudaError_t launch_swiglu(const float*, const float*, float*, int, int, long long, bool, cudaStream_t) { return mock::launched(); }
+cudaError_t launch_moe_route(const unsigned int*, const float*, int, int, const MoeBankEntry*, int, MoeWindow, GroupedProblem*, GroupedProblem*, int*, bool, cudaStream_t) { return mock::launched(); }
+cudaError_t launch_moe_combine(const float*, const float*, const int*, int, int, int, float*, long long, float, float, bool, cudaStream_t, const unsigned int*, int, int) { return mock::launched(); }
 }  // namespace st
