@@ -631,20 +631,26 @@ def run_gpu(args):
     hx_all, hy_all = torch.empty(n_in).pin_memory(), torch.empty(n_out).pin_memory()
     dx_all = torch.empty(n_in, dtype=torch.float32, device="cuda")
     dy_all = torch.empty(n_out, dtype=torch.float32, device="cuda")
-    e2e_plans, spans, oi, oo = [], [], 0, 0  # spans: per shape (plans, input slice, output slice)
+    # launches whose rows travel in one copy each way: a whole shape (chunks of six measured
+    # slower: every chunk boundary breaks the chain of programmatic launches)
+    E2E_CHUNK = CLONES
+    e2e_plans, spans, oi, oo = [], [], 0, 0  # spans: per chunk of one shape (plans, input slice, output slice)
     with torch.cuda.stream(stream):
         for g in groups:
             i_n, o_n = g["layer"].inputs * ROWS, g["layer"].outputs * ROWS
-            i0, o0, first = oi, oo, len(e2e_plans)
-            for w in g["weights"]:
-                hx_all[oi:oi + i_n] = g["hx"].reshape(-1)
-                e2e_plans.append(w.plan(dx_all[oi:oi + i_n].view(ROWS, -1), dy_all[oo:oo + o_n].view(ROWS, -1),
-                                        N.OP_GEMV, stream=stream))
-                oi, oo = oi + i_n, oo + o_n
-            spans.append((e2e_plans[first:], slice(i0, oi), slice(o0, oo)))
+            for c0 in range(0, len(g["weights"]), E2E_CHUNK):
+                i0, o0, first = oi, oo, len(e2e_plans)
+                for w in g["weights"][c0:c0 + E2E_CHUNK]:
+                    hx_all[oi:oi + i_n] = g["hx"].reshape(-1)
+                    e2e_plans.append(w.plan(dx_all[oi:oi + i_n].view(ROWS, -1), dy_all[oo:oo + o_n].view(ROWS, -1),
+                                            N.OP_GEMV, stream=stream))
+                    oi, oo = oi + i_n, oo + o_n
+                spans.append((e2e_plans[first:], slice(i0, oi), slice(o0, oo)))
+    # the widest outputs first: what is still on its way back when the last launch ends is small
+    spans.sort(key=lambda sp: -(sp[2].stop - sp[2].start))
     h2d, d2h = n_in * 4, n_out * 4
-    # Copies are pipelined by shape on a second stream (fork / join inside the capture): the
-    # rows of shape k+1 come in and the rows of shape k-1 go out while shape k computes.
+    # Copies are pipelined by chunk on a second stream (fork / join inside the capture): the
+    # rows of chunk k+1 come in and the rows of chunk k-1 go out while chunk k computes.
     copy_stream = torch.cuda.Stream()
     e2e_graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):
