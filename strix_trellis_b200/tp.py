@@ -51,7 +51,10 @@ def expert_owner(expert_id, experts, world):
     return expert_id // per
 
 
-# ---- collectives at the shard boundary (torch.distributed, NCCL on GPUs, gloo on CPU) ----
+# ---- the shard-boundary steps as library collectives ------------------------------------------
+# For callers that own the exchange themselves (the reference's model) and for the host-side
+# tests, which run them over gloo.  The GPU layers in tp_runtime.py do not use these: their
+# exchange is a kernel that stores into the peers' memory (peer.py).
 def all_reduce_rows(local, group=None):
     """Row-parallel (input-split) recombination: sum of rank outputs, in place."""
     import torch.distributed as dist
