@@ -490,7 +490,7 @@ def run_case(args):
                           "GBps": round(layer.packed_bytes / us / 1e3, 1), "status": ctx.device_status()}))
     elif args.case == "decode":
         # the decoder's own ceiling: decode + mma on tiles resident in shared memory, no memory traffic
-        out = {"case": "decode-rate probe, 16 warps per SM, tiles in shared memory"}
+        out = {"case": "decode-rate probe, 16 warps per SM (and 8 / 32 for K4), tiles in shared memory"}
         sm = torch.cuda.get_device_properties(0).multi_processor_count
         mhz = float(subprocess.run(["nvidia-smi", "--id=0", "--query-gpu=clocks.max.sm", "--format=csv,noheader,nounits"],
                                    capture_output=True, text=True).stdout.strip() or 0)
@@ -499,6 +499,8 @@ def run_case(args):
             clk = w.decode_rate(400)
             out[f"K{bits}"] = {"clocks_per_tile_per_subpartition": round(clk, 1),
                                "GBps_ceiling_at_max_clock": round(4 * sm * mhz * 1e6 / clk * 32 * bits / 1e9, 0)}
+            if bits == 4:  # how much of it is latency that more warps would hide
+                out["K4_warps_per_sm"] = {str(n): round(w.decode_rate(400, warps_per_sm=n), 1) for n in (8, 16, 32)}
             w.close()
         out["sm_max_mhz"] = mhz
         out["status"] = ctx.device_status()

@@ -45,14 +45,16 @@ strix_status strix_b200_core_exact(strix_context context, strix_weights weights,
                                    uint32_t rows, float *core_out, const strix_stream *stream);
 
 /* Decode-rate probe: the fused GEMV's inner loop (production decoder + the same mma) on tiles
- * of these weights held in shared memory, sixteen warps per SM, `iterations` passes, on every
- * SM; no global traffic, barriers or fold.  *clocks_per_tile = SM clocks per 16x16 tile per SM
+ * of these weights held in shared memory, `warps_per_sm` warps per SM (4..32, a multiple of
+ * four; the fused GEMV runs 16), `iterations` passes, on every SM; no global traffic, barriers
+ * or fold.  *clocks_per_tile = SM clocks per 16x16 tile per SM
  * sub-partition: the instruction-issue cost of the decoder and therefore the ceiling of every
  * kernel built on it (bytes/s <= 4 * SMs * clock / clocks_per_tile * bytes per tile).
  * Synchronous; allocates two small buffers.  Counterpart of the reference's decode
  * microbenchmark (src/microbench.hip modes 0-4, bench/README.md:24-31). */
 strix_status strix_b200_decode_rate(strix_context context, strix_weights weights, uint32_t iterations,
-                                    double *clocks_per_tile, const strix_stream *stream);
+                                    uint32_t warps_per_sm, double *clocks_per_tile,
+                                    const strix_stream *stream);
 
 /* K partitions the fused GEMV uses for `rows` rows of these weights (fixes the
  * association of the partial sums; counterpart of linear_split_count,

@@ -76,21 +76,23 @@ strix_status strix_b200_core_exact(strix_context c, strix_weights w, const void*
 }
 
 // Synchronous diagnostic: allocates its two small buffers, runs the probe, waits and averages.
-strix_status strix_b200_decode_rate(strix_context c, strix_weights w, uint32_t iterations, double* clocks_per_tile,
-                                    const strix_stream* stream) {
+strix_status strix_b200_decode_rate(strix_context c, strix_weights w, uint32_t iterations, uint32_t warps_per_sm,
+                                    double* clocks_per_tile, const strix_stream* stream) {
     if (clocks_per_tile) *clocks_per_tile = 0.0;
-    if (!clocks_per_tile || iterations < 1 || iterations > (1u << 20)) return STRIX_ERROR_INVALID_ARGUMENT;
+    if (!clocks_per_tile || iterations < 1 || iterations > (1u << 20) || warps_per_sm < 4 || warps_per_sm > 32 ||
+        warps_per_sm % 4)
+        return STRIX_ERROR_INVALID_ARGUMENT;
     cudaStream_t cs{};
     strix_status s = begin(c, w, stream, cs);
     if (s != STRIX_SUCCESS) return s;
     const int grid = c->sm_count;
     float* sink = nullptr;
     long long* clocks = nullptr;
-    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&sink), (size_t)grid * 512 * sizeof(float));
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&sink), (size_t)grid * warps_per_sm * 32 * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&clocks), (size_t)grid * sizeof(long long));
     std::vector<long long> host(grid);
     for (int pass = 0; pass < 2 && e == cudaSuccess; ++pass)  // the second pass is the measured one
-        e = st::launch_decode_rate(w->device, (int)iterations, grid, sink, clocks, cs);
+        e = st::launch_decode_rate(w->device, (int)iterations, (int)warps_per_sm, grid, sink, clocks, cs);
     if (e == cudaSuccess) e = cudaStreamSynchronize(cs);
     if (e == cudaSuccess) e = cudaMemcpy(host.data(), clocks, (size_t)grid * sizeof(long long), cudaMemcpyDeviceToHost);
     if (sink) (void)cudaFree(sink);
@@ -98,8 +100,8 @@ strix_status strix_b200_decode_rate(strix_context c, strix_weights w, uint32_t i
     if (e != cudaSuccess) { (void)cudaGetLastError(); return cuda_status(e); }
     double total = 0.0;
     for (long long v : host) total += (double)v;
-    // every CTA decodes iterations x 8 tiles per warp on 16 warps, i.e. 4 warps per SM sub-partition
-    *clocks_per_tile = total / grid / ((double)iterations * 8.0 * 16.0 / 4.0);
+    // every CTA decodes iterations x 8 tiles per warp, and a quarter of its warps share an SM sub-partition
+    *clocks_per_tile = total / grid / ((double)iterations * 8.0 * (double)warps_per_sm / 4.0);
     return STRIX_SUCCESS;
 }
 

@@ -82,7 +82,7 @@ cudaError_t launch_core_exact(const DeviceWeights& w, const uint16_t* core16 /*[
 
 // Decode-rate probe: the GEMV's inner loop (decode + mma) on tiles resident in shared memory,
 // `iters` passes over two units on `grid` CTAs of 16 warps; clocks[b] = SM clocks of CTA b.
-cudaError_t launch_decode_rate(const DeviceWeights& w, int iters, int grid, float* sink, long long* clocks,
+cudaError_t launch_decode_rate(const DeviceWeights& w, int iters, int warps, int grid, float* sink, long long* clocks,
                                cudaStream_t stream);
 
 // ---- decode GEMV, rows 1..8, everything fused ---------------------------------------

@@ -244,17 +244,19 @@ static cudaError_t core_exact_bits(const DeviceWeights& w, const uint16_t* a, in
 
 // ---- decode-rate probe ---------------------------------------------------------------------
 // The inner loop of the fused GEMV with nothing around it: two units of the layer's weights sit
-// in shared memory, sixteen warps (column tile = warp % 8, two warps per tile taking turns)
+// in shared memory, 4 to 32 warps per SM (column tile = warp % 8; the fused GEMV runs sixteen)
 // decode them `iters` times with the production device function and feed every tile to the same
 // mma as the GEMV.  No global traffic, no barriers, no fold: the clocks per tile measured here
 // are the instruction-issue cost of the decoder itself, i.e. the ceiling of every kernel that
 // decodes (what the reference measured with modes 0-4 of src/microbench.hip for its own decoder).
 namespace {
-constexpr int kProbeWarps = 16;
+constexpr int kProbeMaxWarps = 32;
 constexpr int kProbeUnits = 2;
 }
-template <int K, int CB>
-__global__ void __launch_bounds__(kProbeWarps * 32) decode_rate_kernel(const DeviceWeights w, int iters, float* sink,
+// kWarps = 16 compiles under the fused GEMV's own thread count (and register room), 32 under
+// the device's maximum.
+template <int K, int CB, int kWarps>
+__global__ void __launch_bounds__(kWarps * 32) decode_rate_kernel(const DeviceWeights w, int iters, float* sink,
                                                                        long long* clocks) {
     extern __shared__ uint32_t probe_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -283,24 +285,31 @@ __global__ void __launch_bounds__(kProbeWarps * 32) decode_rate_kernel(const Dev
     if (threadIdx.x == 0) clocks[blockIdx.x] = t1 - t0;
 }
 
+template <int K, int CB>
+static void probe_launch(const DeviceWeights& w, int iters, int warps, float* sink, long long* clocks, int grid, size_t smem,
+                         cudaStream_t s) {
+    if (warps <= 16) decode_rate_kernel<K, CB, 16><<<grid, warps * 32, smem, s>>>(w, iters, sink, clocks);
+    else decode_rate_kernel<K, CB, kProbeMaxWarps><<<grid, warps * 32, smem, s>>>(w, iters, sink, clocks);
+}
+
 template <int CB>
-static cudaError_t decode_rate_bits(const DeviceWeights& w, int iters, float* sink, long long* clocks, int grid,
+static cudaError_t decode_rate_bits(const DeviceWeights& w, int iters, int warps, float* sink, long long* clocks, int grid,
                                     cudaStream_t s) {
     const size_t smem = (size_t)kProbeUnits * unit_bytes(w.bits);
     switch (w.bits) {
-    case 1: decode_rate_kernel<1, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
-    case 2: decode_rate_kernel<2, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
-    case 3: decode_rate_kernel<3, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
-    case 4: decode_rate_kernel<4, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
-    case 5: decode_rate_kernel<5, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
-    case 6: decode_rate_kernel<6, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
-    case 7: decode_rate_kernel<7, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
-    case 8: decode_rate_kernel<8, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks); break;
+    case 1: probe_launch<1, CB>(w, iters, warps, sink, clocks, grid, smem, s); break;
+    case 2: probe_launch<2, CB>(w, iters, warps, sink, clocks, grid, smem, s); break;
+    case 3: probe_launch<3, CB>(w, iters, warps, sink, clocks, grid, smem, s); break;
+    case 4: probe_launch<4, CB>(w, iters, warps, sink, clocks, grid, smem, s); break;
+    case 5: probe_launch<5, CB>(w, iters, warps, sink, clocks, grid, smem, s); break;
+    case 6: probe_launch<6, CB>(w, iters, warps, sink, clocks, grid, smem, s); break;
+    case 7: probe_launch<7, CB>(w, iters, warps, sink, clocks, grid, smem, s); break;
+    case 8: probe_launch<8, CB>(w, iters, warps, sink, clocks, grid, smem, s); break;
     case 9: case 10: case 11:
         if constexpr (CB == CB_MUL1) {
-            if (w.bits == 9) decode_rate_kernel<9, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks);
-            else if (w.bits == 10) decode_rate_kernel<10, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks);
-            else decode_rate_kernel<11, CB><<<grid, kProbeWarps * 32, smem, s>>>(w, iters, sink, clocks);
+            if (w.bits == 9) probe_launch<9, CB>(w, iters, warps, sink, clocks, grid, smem, s);
+            else if (w.bits == 10) probe_launch<10, CB>(w, iters, warps, sink, clocks, grid, smem, s);
+            else probe_launch<11, CB>(w, iters, warps, sink, clocks, grid, smem, s);
             break;
         }
         return cudaErrorInvalidValue;
@@ -309,14 +318,14 @@ static cudaError_t decode_rate_bits(const DeviceWeights& w, int iters, float* si
     return cudaGetLastError();
 }
 
-// sink: grid * 512 floats, clocks: grid int64 (device memory); clocks[b] = SM clocks CTA b spent in the loop
-cudaError_t launch_decode_rate(const DeviceWeights& w, int iters, int grid, float* sink, long long* clocks,
+// sink: grid * warps * 32 floats, clocks: grid int64 (device memory); clocks[b] = SM clocks CTA b spent in the loop
+cudaError_t launch_decode_rate(const DeviceWeights& w, int iters, int warps, int grid, float* sink, long long* clocks,
                                cudaStream_t stream) {
-    if (iters < 1 || grid < 1) return cudaErrorInvalidValue;
+    if (iters < 1 || grid < 1 || warps < 4 || warps > kProbeMaxWarps || warps % 4) return cudaErrorInvalidValue;
     switch (w.codebook) {
-    case CB_3INST: return decode_rate_bits<CB_3INST>(w, iters, sink, clocks, grid, stream);
-    case CB_MCG: return decode_rate_bits<CB_MCG>(w, iters, sink, clocks, grid, stream);
-    case CB_MUL1: return decode_rate_bits<CB_MUL1>(w, iters, sink, clocks, grid, stream);
+    case CB_3INST: return decode_rate_bits<CB_3INST>(w, iters, warps, sink, clocks, grid, stream);
+    case CB_MCG: return decode_rate_bits<CB_MCG>(w, iters, warps, sink, clocks, grid, stream);
+    case CB_MUL1: return decode_rate_bits<CB_MUL1>(w, iters, warps, sink, clocks, grid, stream);
     default: return cudaErrorInvalidValue;
     }
 }

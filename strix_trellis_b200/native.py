@@ -217,7 +217,7 @@ PROTOTYPES = {
     "strix_b200_input_stages": (C.c_int, [vp, vp, vp, u32, vp, vp, vp, P(Stream)]),
     "strix_b200_output_stages": (C.c_int, [vp, vp, vp, u32, u32, f32, f32, vp, P(Stream)]),
     "strix_b200_core_exact": (C.c_int, [vp, vp, vp, u32, vp, P(Stream)]),
-    "strix_b200_decode_rate": (C.c_int, [vp, vp, u32, P(C.c_double), P(Stream)]),
+    "strix_b200_decode_rate": (C.c_int, [vp, vp, u32, u32, P(C.c_double), P(Stream)]),
     "strix_b200_gemv_splits": (C.c_int, [vp, vp, u32, P(u32)]),
     "strix_b200_gemv_partition": (C.c_int, [u64, u64, u32, u32, u64, P(u64)]),
     "strix_b200_moe_combine": (C.c_int, [vp, vp, vp, u32, u32, u32, vp, u64, f32, f32, P(Stream)]),

@@ -229,12 +229,12 @@ class Weights:
                                                out.data_ptr(), C.byref(sd)), "strix_b200_core_exact")
         return out
 
-    def decode_rate(self, iterations=200, stream=None):
+    def decode_rate(self, iterations=200, warps_per_sm=16, stream=None):
         """SM clocks per 16x16 tile per SM sub-partition of the decode + mma loop alone."""
         out = C.c_double()
         sd = _cur_stream(stream)
-        N.check(self.lib.strix_b200_decode_rate(self.ctx.handle, self.handle, iterations, C.byref(out), C.byref(sd)),
-                "strix_b200_decode_rate")
+        N.check(self.lib.strix_b200_decode_rate(self.ctx.handle, self.handle, iterations, warps_per_sm, C.byref(out),
+                                                C.byref(sd)), "strix_b200_decode_rate")
         return out.value
 
     def gemv_splits(self, rows):

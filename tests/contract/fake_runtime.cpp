@@ -121,7 +121,7 @@ cudaError_t launch_dequantize(const DeviceWeights&, uint16_t*, cudaStream_t) { r
 cudaError_t launch_input_stages(const DeviceWeights&, const float*, long long, int, uint16_t*, float*, uint16_t*, cudaStream_t) { return mock::launched(); }
 cudaError_t launch_output_stages(const DeviceWeights&, const float*, int, int, float*, long long, float, float, cudaStream_t) { return mock::launched(); }
 cudaError_t launch_core_exact(const DeviceWeights&, const uint16_t*, int, float*, cudaStream_t) { return mock::launched(); }
-cudaError_t launch_decode_rate(const DeviceWeights&, int, int, float*, long long*, cudaStream_t) { return mock::launched(); }
+cudaError_t launch_decode_rate(const DeviceWeights&, int, int, int, float*, long long*, cudaStream_t) { return mock::launched(); }
 GemvPlan plan_gemv(const DeviceWeights& w, int rows, int) {
     GemvPlan p{};
     p.grid = 4; p.splits = 2; p.stages = 2; p.act_blocks = 1;
