@@ -458,3 +458,19 @@ def test_rejections_with_the_real_driver(ctx):
     want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, None, 2, 2, host(x))
     gate(host(got), want, "deep K global fold")
     w.close()
+
+
+def test_decode_rate_probe_reports_a_plausible_cost(ctx):
+    """The decoder-only probe: a positive, finite number of SM clocks per tile for every rate and
+    warp count it accepts (the decoder of any rate needs more than 20 and far fewer than 400
+    clocks), and a refusal for warp counts that do not fill the SM's four sub-partitions evenly."""
+    for bits in (2, 4, 5):
+        w = ctx.prepare(synthetic.make_layer(256, 256, bits, 4400 + bits))
+        for warps in (8, 16, 32):
+            clocks = w.decode_rate(20, warps_per_sm=warps)
+            assert 20.0 < clocks < 400.0, (bits, warps, clocks)
+        for bad in (0, 2, 18, 36):
+            with pytest.raises(N.StrixError):
+                w.decode_rate(20, warps_per_sm=bad)
+        w.close()
+    assert ctx.device_status() == 0
