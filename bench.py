@@ -706,6 +706,56 @@ def run_gpu(args):
     clocks.__exit__()
     clock_summary = clocks.summary()
 
+    # ---- the same step as two and four independent chains of launches on as many streams ----
+    # Reported beside the headline, not as it: a launch of the headline chain starts when the
+    # one before it has ended; here copy i runs on chain i % chains, so one chain's launch
+    # decodes while another chain's launch is in its fold tail -- what a caller with
+    # independent projections (q/k/v, gate/up, experts) gets.
+    two_chains = None
+    if not args.no_extra and rank == 0:
+        two_chains = {}
+        for chains in (2, 4):
+            side = [torch.cuda.Stream() for _ in range(chains - 1)]
+            for g in groups:
+                g["y_side"], g["plans_side"] = [], {}
+                for k, st2 in enumerate(side):
+                    with torch.cuda.stream(st2):
+                        yb = torch.zeros_like(g["y"])
+                        g["y_side"].append(yb)
+                        for i in range(k + 1, len(g["weights"]), chains):  # copy i runs on chain i % chains
+                            g["plans_side"][i] = g["weights"][i].plan(g["x"], yb, N.OP_GEMV, stream=st2)
+                        st2.synchronize()
+            multi = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                with torch.cuda.graph(multi, stream=stream):
+                    for st2 in side:
+                        st2.wait_stream(stream)  # fork
+                    for g in groups:
+                        for i in range(len(g["weights"])):
+                            (g["plans"][i] if i % chains == 0 else g["plans_side"][i]).submit()
+                    for st2 in side:
+                        stream.wait_stream(st2)  # join
+                for _ in range(3):
+                    multi.replay()
+                stream.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                for _ in range(args.steps):
+                    multi.replay()
+                b.record(stream)
+                stream.synchronize()
+                multi_ms = a.elapsed_time(b) / args.steps
+            for g in groups:
+                for yb in g["y_side"]:
+                    if not torch.equal(yb, g["y"]):
+                        raise SystemExit("multi-chain run: output row differs from the single-chain row")
+                for q in g["plans_side"].values():
+                    q.close()
+                g["y_side"], g["plans_side"] = [], {}
+            two_chains[f"chains{chains}"] = {"GBps": round(total_bytes / (multi_ms * 1e-3) / 1e9, 1),
+                                             "ms_per_step": round(multi_ms, 4)}
+            del multi
+
     # ---- the other configurations of the metric, outside the timed region above ----------
     for g in groups:  # free the clone rotations first
         for p in g["plans"]:
@@ -718,6 +768,7 @@ def run_gpu(args):
         if (ROOT / "MEASURED_PEAKS.json").exists():
             gemm_peak = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"])
         if rank == 0:
+            extra["gemv_sweep_independent_chains"] = two_chains
             gemm = gemm_case(torch, ctx, stream, [128, 512, 2048, 8192])
             for v in gemm.values():
                 v["frac_of_measured_dense_peak"] = round(v["TFLOPs"] / gemm_peak, 3)
