@@ -157,15 +157,25 @@ __global__ void __launch_bounds__(kThreads) peer_sum_kernel(const ReduceArgs a) 
     const uint4* slots = reinterpret_cast<const uint4*>(a.view.arena[t.rank]) + slot0;
     bool late = false;
     for (long long i = lane0; i < a.count2 && !late; i += step) {
+        // all ranks' words of this pair are asked for at once; only those that have not landed
+        // yet are asked for again
+        uint4 part[kRanks];
+#pragma unroll
+        for (int r = 0; r < kRanks; ++r)
+            if (r < a.view.world) part[r] = ld_sys_v4(slots + (long long)r * a.count2 + i);
         float s0 = 0.f, s1 = 0.f;  // ascending rank order from +0, on every rank
-        for (int r = 0; r < a.view.world && !late; ++r) {
-            uint4 part = ld_sys_v4(slots + (long long)r * a.count2 + i);
-            for (uint32_t tries = 0; (part.y != t.epoch || part.w != t.epoch) && !late; ++tries) {
-                if (tries >= a.view.wait_polls) late = true;  // bounded
-                else part = ld_sys_v4(slots + (long long)r * a.count2 + i);
+#pragma unroll
+        for (int r = 0; r < kRanks; ++r) {
+            if (r >= a.view.world || late) continue;
+            for (uint32_t tries = 0; part[r].y != t.epoch || part[r].w != t.epoch; ++tries) {
+                if (tries >= a.view.wait_polls) {  // bounded
+                    late = true;
+                    break;
+                }
+                part[r] = ld_sys_v4(slots + (long long)r * a.count2 + i);
             }
-            s0 = __fadd_rn(s0, __uint_as_float(part.x));
-            s1 = __fadd_rn(s1, __uint_as_float(part.z));
+            s0 = __fadd_rn(s0, __uint_as_float(part[r].x));
+            s1 = __fadd_rn(s1, __uint_as_float(part[r].z));
         }
         if (!late) y[i] = make_float2(s0, s1);
     }
