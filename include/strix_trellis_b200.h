@@ -184,6 +184,11 @@ strix_status strix_b200_peer_sum(strix_b200_peer_group group, float *const *rows
  * result[i] != NULL receives a private contiguous copy; with NULL the result is read in the
  * arena at region + parity * total_rows * total_cols * 4.  Region size per matrix:
  * 2 * total_rows * total_cols * 4 bytes. */
+/* flags: with STRIX_B200_PEER_GATHER_TAGGED every word travels with the exchange number beside
+ * it (8 bytes per word, no fence and no flag step: the lowest latency).  Then every matrix needs
+ * a result pointer, even widths, column offsets and total_cols, and a region of
+ * 2 * total_rows * total_cols * 8 bytes. */
+#define STRIX_B200_PEER_GATHER_TAGGED 1u
 typedef struct strix_b200_peer_matrix {
     const void *block[STRIX_B200_PEER_MAX_RANKS];  /* per local rank */
     void *result[STRIX_B200_PEER_MAX_RANKS];       /* per local rank, or NULL */
@@ -196,7 +201,7 @@ typedef struct strix_b200_peer_gather_desc {
     uint32_t struct_size;
     uint32_t abi_version;
     uint32_t matrices; /* 1..3 */
-    uint32_t flags;    /* zero */
+    uint32_t flags;    /* zero or STRIX_B200_PEER_GATHER_TAGGED */
     uint32_t rows[STRIX_B200_PEER_MAX_RANKS];   /* per rank */
     uint32_t row_at[STRIX_B200_PEER_MAX_RANKS]; /* per rank */
     strix_b200_peer_matrix matrix[3];

@@ -258,6 +258,71 @@ __global__ void __launch_bounds__(kThreads) peer_gather_kernel(const GatherArgs 
     exchange_end(t);
 }
 
+// The same exchange without the fence and the flag step, for results that are copied out anyway:
+// every pair of words travels as {word, epoch, word, epoch} (16 bytes, not torn as two 8-byte
+// halves), the receiver spins on the words of every rank's block while it copies them out.  The
+// region holds [2 parities][total_rows][total_cols] words x 8 bytes.  Widths, column offsets and
+// total_cols are even.
+__global__ void __launch_bounds__(kThreads) peer_gather_tagged_kernel(const GatherArgs a) {
+    __shared__ int s_late;
+    const Turn t = exchange_begin(a.view);
+    if (threadIdx.x == 0) s_late = 0;
+    const long long lane0 = (long long)blockIdx.x * kThreads + threadIdx.x, step = (long long)kCtas * kThreads;
+    for (int m = 0; m < a.matrices; ++m) {
+        const int width2 = a.width[m][t.rank] / 2, total2 = a.total_cols[m] / 2;
+        const long long pairs = (long long)a.rows[t.rank] * width2;
+        const long long base = (long long)(a.region[m] / 16) + (long long)t.parity() * a.total_rows * total2;
+        const uint2* src = reinterpret_cast<const uint2*>(a.block[m][blockIdx.y]);
+        for (long long i = lane0; i < pairs; i += step) {
+            const long long row = i / width2, col2 = i - row * width2;
+            const uint2 value = src[i];
+            const uint4 word = make_uint4(value.x, t.epoch, value.y, t.epoch);
+            const long long at = base + (a.row_at[t.rank] + row) * total2 + a.col_at[m][t.rank] / 2 + col2;
+            for (int p = 0; p < a.view.world; ++p) st_sys_v4(reinterpret_cast<uint4*>(a.view.arena[p]) + at, word);
+        }
+    }
+    bool late = false;
+    for (int m = 0; m < a.matrices && !late; ++m) {
+        const int total2 = a.total_cols[m] / 2;
+        const uint4* landed = reinterpret_cast<const uint4*>(a.view.arena[t.rank]) + a.region[m] / 16 +
+                              (long long)t.parity() * a.total_rows * total2;
+        uint2* out = reinterpret_cast<uint2*>(a.result[m][blockIdx.y]);
+        for (int r = 0; r < a.view.world && !late; ++r) {  // rank r's block, wherever it lands
+            const int width2 = a.width[m][r] / 2;
+            const long long pairs = (long long)a.rows[r] * width2;
+            const long long origin = (long long)a.row_at[r] * total2 + a.col_at[m][r] / 2;
+            for (long long i0 = lane0; i0 < pairs && !late; i0 += 4 * step) {
+                uint4 part[4];   // four pairs asked for at once; those not landed yet are asked for again
+                long long at[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const long long i = i0 + u * step;
+                    const long long row = i / width2;
+                    at[u] = origin + row * total2 + (i - row * width2);
+                    if (i < pairs) part[u] = ld_sys_v4(landed + at[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (i0 + u * step >= pairs || late) continue;
+                    for (uint32_t tries = 0; part[u].y != t.epoch || part[u].w != t.epoch; ++tries) {
+                        if (tries >= a.view.wait_polls) {  // bounded
+                            late = true;
+                            break;
+                        }
+                        part[u] = ld_sys_v4(landed + at[u]);
+                    }
+                    if (!late) out[at[u]] = make_uint2(part[u].x, part[u].z);
+                }
+            }
+        }
+    }
+    if (late) {
+        if (a.view.status) atomicOr(a.view.status, kTimeoutPeer);
+        s_late = 1;
+    }
+    exchange_end(t);
+}
+
 // ---- routed rows back to the home rank of their token -----------------------------------------
 // Tokens are laid out rank-major: token t lives on rank t / tokens_per_rank.  A rank that owns
 // the expert of route (t, s) -- id inside its window [first_expert, first_expert + experts) --
@@ -439,7 +504,9 @@ strix_status strix_b200_peer_gather(strix_b200_peer_group g, const strix_b200_pe
     if (s != STRIX_SUCCESS) return s;
     s = header(d);
     if (s != STRIX_SUCCESS) return s;
-    if (d->matrices < 1 || d->matrices > (uint32_t)kSegments) return STRIX_ERROR_INVALID_ARGUMENT;
+    if (d->matrices < 1 || d->matrices > (uint32_t)kSegments || (d->flags & ~(uint32_t)STRIX_B200_PEER_GATHER_TAGGED))
+        return STRIX_ERROR_INVALID_ARGUMENT;
+    const bool tagged = (d->flags & STRIX_B200_PEER_GATHER_TAGGED) != 0;
     GatherArgs a{};
     a.view = g->view;
     a.matrices = (int)d->matrices;
@@ -457,9 +524,12 @@ strix_status strix_b200_peer_gather(strix_b200_peer_group g, const strix_b200_pe
         if (mx.total_cols < 1 || mx.total_cols > INT_MAX) return STRIX_ERROR_INVALID_ARGUMENT;
         a.total_cols[m] = (int)mx.total_cols;
         a.region[m] = mx.region;
-        if (!region_fits(g, mx.region, 2ull * total_rows * mx.total_cols * 4)) return STRIX_ERROR_INSUFFICIENT_BUFFER;
+        if (!region_fits(g, mx.region, 2ull * total_rows * mx.total_cols * (tagged ? 8 : 4)))
+            return STRIX_ERROR_INSUFFICIENT_BUFFER;
+        if (tagged && mx.total_cols % 2) return STRIX_ERROR_INVALID_ARGUMENT;
         for (int r = 0; r < g->view.world; ++r) {
             if ((uint64_t)mx.col_at[r] + mx.width[r] > mx.total_cols) return STRIX_ERROR_INVALID_ARGUMENT;
+            if (tagged && (mx.width[r] % 2 || mx.col_at[r] % 2)) return STRIX_ERROR_INVALID_ARGUMENT;
             a.width[m][r] = (int)mx.width[r];
             a.col_at[m][r] = (int)mx.col_at[r];
         }
@@ -468,11 +538,13 @@ strix_status strix_b200_peer_gather(strix_b200_peer_group g, const strix_b200_pe
             if ((!mx.block[i] && a.rows[r] && a.width[m][r]) || reinterpret_cast<uintptr_t>(mx.block[i]) % 16 ||
                 reinterpret_cast<uintptr_t>(mx.result[i]) % 16)
                 return STRIX_ERROR_INVALID_ARGUMENT;
+            if (tagged && !mx.result[i]) return STRIX_ERROR_INVALID_ARGUMENT;  // tagged words are of no use in place
             a.block[m][i] = static_cast<const uint32_t*>(mx.block[i]);
             a.result[m][i] = static_cast<uint32_t*>(mx.result[i]);
         }
     }
-    peer_gather_kernel<<<dim3(kCtas, g->local_count), kThreads, 0, cs>>>(a);
+    if (tagged) peer_gather_tagged_kernel<<<dim3(kCtas, g->local_count), kThreads, 0, cs>>>(a);
+    else peer_gather_kernel<<<dim3(kCtas, g->local_count), kThreads, 0, cs>>>(a);
     return cuda_status(cudaGetLastError());
 }
 

@@ -133,6 +133,7 @@ P = C.POINTER
 # name -> (restype, argtypes).  Every symbol declared in include/*.h is listed here;
 # tests check that the library exports each of them.
 PEER_RANKS, PEER_HANDLE_BYTES, PEER_CONTROL_BYTES = 8, 64, 2304
+PEER_GATHER_TAGGED = 1
 
 
 class PeerMatrix(C.Structure):

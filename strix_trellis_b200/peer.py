@@ -82,11 +82,14 @@ class PeerGroup:
         N.check(self.lib.strix_b200_peer_sum(self.handle, ptrs, rows[0].numel(), region, C.byref(sd)),
                 "strix_b200_peer_sum")
 
-    def gather(self, rows, row_at, matrices, stream=None):
+    def gather(self, rows, row_at, matrices, stream=None, tagged=False):
         """matrices: up to three dicts with `blocks` (one tensor of 32-bit words per local rank),
-        `results` (same, or None), `widths`, `col_at` (per rank), `total_cols`, `region`."""
+        `results` (same, or None), `widths`, `col_at` (per rank), `total_cols`, `region`.
+        `tagged`: every word travels with the exchange number (no fence, no flag step); needs
+        results, even widths and a region for 8 bytes per word."""
         d = N.PeerGatherDesc()
         d.struct_size, d.abi_version, d.matrices = C.sizeof(d), N.ABI_VERSION, len(matrices)
+        d.flags = N.PEER_GATHER_TAGGED if tagged else 0
         for r in range(self.world):
             d.rows[r], d.row_at[r] = rows[r], row_at[r]
         for m, spec in enumerate(matrices):

@@ -44,27 +44,28 @@ def test_sum_is_rank_ordered_and_identical_on_every_rank(ctx, world):
     g.close()
 
 
-def test_gather_uneven_column_blocks_and_row_blocks(ctx):
+@pytest.mark.parametrize("tagged", [False, True])
+def test_gather_uneven_column_blocks_and_row_blocks(ctx, tagged):
     world = 4
     g = PeerGroup(ctx, 8 << 20, rank=0, world=world, local_ranks=world)
     rng = np.random.default_rng(5)
     # column blocks of uneven width (an LM head whose block count does not divide by the ranks)
     widths, rows = [384, 256, 256, 128], 3
     col_at = [0, 384, 640, 896]
-    region = g.reserve(rows * 1024 * 4)
+    region = g.reserve(rows * 1024 * (8 if tagged else 4))
     for turn in range(3):
         blocks = [rng.normal(size=(rows, w)).astype(np.float32) for w in widths]
         outs = [torch.zeros((rows, 1024), device="cuda") for _ in range(world)]
         g.gather([rows] * world, [0] * world,
                  [dict(blocks=[dev(b) for b in blocks], results=outs, widths=widths, col_at=col_at, total_cols=1024,
-                       region=region)])
+                       region=region)], tagged=tagged)
         torch.cuda.synchronize()
         want = np.concatenate(blocks, axis=1)
         for r in range(world):
             assert host(outs[r]).tobytes() == want.tobytes(), (turn, r)
     # row blocks of three matrices at once (token rows, route ids, scores); narrow ones are 6 words wide
     per, model, k = 5, 256, 6
-    regions = [g.reserve(world * per * w * 4) for w in (model, k, k)]
+    regions = [g.reserve(world * per * w * (8 if tagged else 4)) for w in (model, k, k)]
     xs = [rng.normal(size=(per, model)).astype(np.float32) for _ in range(world)]
     ids = [rng.integers(0, 1000, (per, k)).astype(np.int32) for _ in range(world)]
     sc = [rng.random((per, k)).astype(np.float32) for _ in range(world)]
@@ -72,7 +73,7 @@ def test_gather_uneven_column_blocks_and_row_blocks(ctx):
            for w, t in ((model, torch.float32), (k, torch.int32), (k, torch.float32))]
     mats = [dict(blocks=[dev(b) for b in src], results=res[m], widths=[w] * world, col_at=[0] * world, total_cols=w,
                  region=regions[m]) for m, (src, w) in enumerate(((xs, model), (ids, k), (sc, k)))]
-    g.gather([per] * world, [r * per for r in range(world)], mats)
+    g.gather([per] * world, [r * per for r in range(world)], mats, tagged=tagged)
     torch.cuda.synchronize()
     for r in range(world):
         assert host(res[0][r]).tobytes() == np.concatenate(xs).tobytes()
