@@ -410,8 +410,12 @@ strix_status create_device(strix_context c, const strix_tp_moe_device_desc* d, c
     p->down_count = routes;
     p->bank_count = (int)d->expert_count;
     p->window = st::MoeWindow{0, p->bank_count};
-    p->gu_plan = st::plan_grouped(g.model, g.inter, g.max_bits, p->gu_count, c->sm_count);
-    p->down_plan = st::plan_grouped(g.inter, g.model, g.max_bits, p->down_count, c->sm_count);
+    // the K partition is planned for the problems a step is EXPECTED to have (routes spread evenly
+    // over the bank, eight rows per problem), not for the slots it may have at most
+    const int spread = std::min(routes, p->bank_count * ((routes + p->bank_count * st::kGroupRows - 1) /
+                                                        (p->bank_count * st::kGroupRows)));
+    p->gu_plan = st::plan_grouped(g.model, g.inter, g.max_bits, 2 * spread, c->sm_count);
+    p->down_plan = st::plan_grouped(g.inter, g.model, g.max_bits, spread, c->sm_count);
     const size_t bytes = layout_block(p, p->gu_count, p->down_count, false);
     cudaError_t e = cudaMalloc(&p->block, bytes);
     if (e != cudaSuccess) { (void)cudaGetLastError(); delete p; return cuda_status(e); }

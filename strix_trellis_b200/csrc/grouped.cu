@@ -197,15 +197,17 @@ GroupedPlan plan_grouped(int inputs, int outputs, int max_bits, int problems, in
     const int hblocks = inputs / 128, nblocks = outputs / 128;
     const int cap = 32;  // H128 blocks of K per CTA: 8 rows x 32 blocks x 256 B = 64 KB of core input
     const int min_splits = (hblocks + cap - 1) / cap;
-    // Two CTAs fit an SM.  Among the K partition counts, take the one with the least
-    // (waves of CTAs) x (units per CTA + a fixed cost of about four units per CTA).
+    // Among the K partition counts, take the one with the least estimated time in units of
+    // one decoded unit on one SM: the CTAs' work spread over the SMs (two CTAs share an SM and its
+    // issue slots; a CTA costs about one unit beyond its own) plus the half-empty tail of the last
+    // CTAs.  `problems` is the number of problems the caller EXPECTS to be live.  Fitted to the
+    // routed-expert block at 1 / 8 / 64 tokens, where 2-4 / 2 / 1 partitions measured best.
     int splits = min_splits;
-    long long best = -1;
+    double best = -1.0;
     for (int s = min_splits; s <= hblocks && s <= 16; s *= 2) {
-        const long long ctas = (long long)problems * nblocks * s;
-        const long long waves = (ctas + 2LL * sm_count - 1) / (2LL * sm_count);
-        const long long cost = waves * ((hblocks + s - 1) / s + 4);
-        if (best < 0 || cost < best) { best = cost; splits = s; }
+        const double ctas = (double)problems * nblocks * s, each = (double)((hblocks + s - 1) / s) + 1.0;
+        const double cost = ctas * each / sm_count + 0.5 * each;
+        if (best < 0.0 || cost < best) { best = cost; splits = s; }
     }
     const int per = (hblocks + splits - 1) / splits;
     int stages = (32 * 1024) / unit_bytes(max_bits);
