@@ -174,3 +174,28 @@ def test_expert_windows_recombine_to_the_single_rank_block(ctx):
     for t in ws:
         for w in t:
             w.close()
+
+
+def test_gather_descriptor_rules(ctx):
+    """What the gather refuses: a region that does not fit the arena, a block that sticks out of
+    the matrix, and -- for tagged words -- odd widths or a missing result."""
+    world = 2
+    g = PeerGroup(ctx, 1 << 20, rank=0, world=world, local_ranks=world)
+    region = g.reserve(4 * 256 * 8)
+    blocks = [torch.zeros((4, 128), device="cuda") for _ in range(world)]
+    outs = [torch.zeros((4, 256), device="cuda") for _ in range(world)]
+    good = dict(blocks=blocks, results=outs, widths=[128, 128], col_at=[0, 128], total_cols=256, region=region)
+    g.gather([4, 4], [0, 0], [good], tagged=True)
+    torch.cuda.synchronize()
+    bad = [dict(good, region=(1 << 20) + 4096),                 # outside the arena
+           dict(good, col_at=[0, 192]),                         # second block sticks out
+           dict(good, widths=[127, 128]),                       # odd width with tagged words
+           dict(good, results=[None, None])]                    # tagged words are of no use in place
+    for spec in bad:
+        with pytest.raises(N.StrixError):
+            g.gather([4, 4], [0, 0], [spec], tagged=True)
+    with pytest.raises(N.StrixError):
+        g.set_wait_polls(0)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    g.close()
