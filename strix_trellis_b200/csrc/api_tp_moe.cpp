@@ -17,7 +17,7 @@ struct strix_tp_moe_plan_impl {
     strix_context owner = nullptr;
     cudaStream_t stream{};
     std::vector<strix_weights> retained;
-    int tokens = 0, top_k = 0, model = 0, inter = 0, codebook = 2;
+    int tokens = 0, top_k = 0, model = 0, inter = 0, codebook = 2, max_bits = 0;
     bool device_routed = false;
     void* block = nullptr;  // one plan-owned device allocation
     st::GroupedProblem *gu = nullptr, *down = nullptr;
@@ -113,6 +113,14 @@ struct Carver {  // bump allocator over one device block (sizes only when base =
         return p;
     }
 };
+
+// Problems a step is expected to have when `routes` routes spread evenly over `bank` experts,
+// eight rows per problem.
+int expected_problems(int routes, int bank) {
+    if (routes < 1) routes = 1;
+    const int chunks = (routes + bank * st::kGroupRows - 1) / (bank * st::kGroupRows);
+    return std::min(routes, bank * chunks);
+}
 
 void fill_problem(st::GroupedProblem& p, const st::DeviceWeights& w, const float* x, long long xs, float* y,
                   long long ys, unsigned int* counters, float* partials) {
@@ -412,10 +420,18 @@ strix_status create_device(strix_context c, const strix_tp_moe_device_desc* d, c
     p->window = st::MoeWindow{0, p->bank_count};
     // the K partition is planned for the problems a step is EXPECTED to have (routes spread evenly
     // over the bank, eight rows per problem), not for the slots it may have at most
-    const int spread = std::min(routes, p->bank_count * ((routes + p->bank_count * st::kGroupRows - 1) /
-                                                        (p->bank_count * st::kGroupRows)));
-    p->gu_plan = st::plan_grouped(g.model, g.inter, g.max_bits, 2 * spread, c->sm_count);
-    p->down_plan = st::plan_grouped(g.inter, g.model, g.max_bits, spread, c->sm_count);
+    const int spread = expected_problems(routes, p->bank_count);
+    p->max_bits = g.max_bits;
+    // Scratch for up to four times the planned partitions (while it stays under 128 MB): a
+    // window set later means fewer local routes, and fewer problems want more partitions.
+    int headroom = 4;
+    for (;; headroom /= 2) {
+        p->gu_plan = st::plan_grouped(g.model, g.inter, g.max_bits, 2 * spread, c->sm_count, headroom);
+        p->down_plan = st::plan_grouped(g.inter, g.model, g.max_bits, spread, c->sm_count, headroom);
+        const size_t scratch = (size_t)p->gu_count * p->gu_plan.partial_bytes_per_problem +
+                               (size_t)p->down_count * p->down_plan.partial_bytes_per_problem;
+        if (headroom == 1 || scratch <= ((size_t)128 << 20)) break;
+    }
     const size_t bytes = layout_block(p, p->gu_count, p->down_count, false);
     cudaError_t e = cudaMalloc(&p->block, bytes);
     if (e != cudaSuccess) { (void)cudaGetLastError(); delete p; return cuda_status(e); }
@@ -539,6 +555,13 @@ strix_status strix_b200_moe_plan_set_window(strix_tp_moe_plan p, uint32_t first_
     if (experts_total > INT_MAX || (uint64_t)first_expert + (uint64_t)p->bank_count > experts_total)
         return STRIX_ERROR_INVALID_ARGUMENT;
     p->window = st::MoeWindow{(int)first_expert, (int)experts_total};
+    // of all routes, about bank / experts_total are this rank's: plan the partitions for those
+    const long long routes = (long long)p->tokens * p->top_k;
+    const int local = (int)std::max<long long>(1, (routes * p->bank_count + experts_total - 1) / experts_total);
+    const int spread = expected_problems(local, p->bank_count);
+    const int sms = p->owner->sm_count;
+    p->gu_plan = st::replan_grouped(p->gu_plan, p->model, p->inter, p->max_bits, 2 * spread, sms);
+    p->down_plan = st::replan_grouped(p->down_plan, p->inter, p->model, p->max_bits, spread, sms);
     return STRIX_SUCCESS;
 }
 // Routing, gate/up, SwiGLU and down of the routes this rank owns; no combine.

@@ -17,6 +17,7 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kThreadsG = (kWarps + 1) * 32;
 constexpr int kMaxStages = 16;
+constexpr int kMaxSplits = 16;
 constexpr size_t kGroupedSmemLimit = 110 * 1024;  // dynamic shared memory a launch may ask for (two CTAs per SM)
 
 struct GroupedArgs {
@@ -192,23 +193,28 @@ __global__ void __launch_bounds__(kThreadsG, 2) grouped_linear_kernel(const Grou
     }
 }
 
-GroupedPlan plan_grouped(int inputs, int outputs, int max_bits, int problems, int sm_count) {
-    GroupedPlan plan{};
-    const int hblocks = inputs / 128, nblocks = outputs / 128;
-    const int cap = 32;  // H128 blocks of K per CTA: 8 rows x 32 blocks x 256 B = 64 KB of core input
-    const int min_splits = (hblocks + cap - 1) / cap;
-    // Among the K partition counts, take the one with the least estimated time in units of
-    // one decoded unit on one SM: the CTAs' work spread over the SMs (two CTAs share an SM and its
-    // issue slots; a CTA costs about one unit beyond its own) plus the half-empty tail of the last
-    // CTAs.  `problems` is the number of problems the caller EXPECTS to be live.  Fitted to the
-    // routed-expert block at 1 / 8 / 64 tokens, where 2-4 / 2 / 1 partitions measured best.
+namespace {
+constexpr int kBlocksPerCta = 32;  // H128 blocks of K per CTA: 8 rows x 32 blocks x 256 B = 64 KB of core input
+
+// Among the K partition counts up to `most`, the one with the least estimated time in units of
+// one decoded unit on one SM: the CTAs' work spread over the SMs (two CTAs share an SM and its
+// issue slots; a CTA costs about one unit beyond its own) plus the half-empty tail of the last
+// CTAs.  `problems` is the number of problems the caller EXPECTS to be live.  Fitted to the
+// routed-expert block at 1 / 8 / 64 tokens, where 2-4 / 2 / 1 partitions measured best.
+int choose_splits(int hblocks, int nblocks, int problems, int sm_count, int most) {
+    const int min_splits = (hblocks + kBlocksPerCta - 1) / kBlocksPerCta;
     int splits = min_splits;
     double best = -1.0;
-    for (int s = min_splits; s <= hblocks && s <= 16; s *= 2) {
+    for (int s = min_splits; s <= hblocks && s <= most; s *= 2) {
         const double ctas = (double)problems * nblocks * s, each = (double)((hblocks + s - 1) / s) + 1.0;
         const double cost = ctas * each / sm_count + 0.5 * each;
         if (best < 0.0 || cost < best) { best = cost; splits = s; }
     }
+    return splits;
+}
+
+// Everything of a plan that follows from its partition count.
+void shape_plan(GroupedPlan& plan, int hblocks, int nblocks, int max_bits, int splits) {
     const int per = (hblocks + splits - 1) / splits;
     int stages = (32 * 1024) / unit_bytes(max_bits);
     if (stages > per) stages = per;
@@ -219,8 +225,28 @@ GroupedPlan plan_grouped(int inputs, int outputs, int max_bits, int problems, in
     plan.ctas_per_problem = nblocks * splits;
     plan.stage_stride = unit_bytes(max_bits);
     plan.smem_bytes = 256 + (size_t)stages * plan.stage_stride + (size_t)per * 256 * kGroupRows;
+}
+}  // namespace
+
+GroupedPlan plan_grouped(int inputs, int outputs, int max_bits, int problems, int sm_count, int headroom) {
+    GroupedPlan plan{};
+    const int hblocks = inputs / 128, nblocks = outputs / 128;
+    const int splits = choose_splits(hblocks, nblocks, problems, sm_count, kMaxSplits);
+    shape_plan(plan, hblocks, nblocks, max_bits, splits);
+    int room = splits * (headroom < 1 ? 1 : headroom);  // partitions the scratch is sized for
+    if (room > kMaxSplits) room = kMaxSplits;
+    if (room > hblocks) room = hblocks;
+    if (room < splits) room = splits;
+    plan.scratch_splits = room;
     plan.counter_bytes_per_problem = align_up((size_t)nblocks * sizeof(unsigned int));
-    plan.partial_bytes_per_problem = align_up((size_t)nblocks * splits * kGroupRows * 128 * sizeof(float));
+    plan.partial_bytes_per_problem = align_up((size_t)nblocks * room * kGroupRows * 128 * sizeof(float));
+    return plan;
+}
+
+GroupedPlan replan_grouped(const GroupedPlan& sized, int inputs, int outputs, int max_bits, int problems, int sm_count) {
+    GroupedPlan plan = sized;  // the scratch figures stay: they describe memory that exists
+    const int hblocks = inputs / 128, nblocks = outputs / 128;
+    shape_plan(plan, hblocks, nblocks, max_bits, choose_splits(hblocks, nblocks, problems, sm_count, sized.scratch_splits));
     return plan;
 }
 

@@ -23,7 +23,8 @@ struct GroupedProblem {
 };
 
 struct GroupedPlan {
-    int splits;
+    int splits;          // K partitions per column block of a launch
+    int scratch_splits;  // partitions the per-problem scratch is sized for (>= splits)
     int stages;
     int ctas_per_problem;
     int stage_stride;
@@ -31,7 +32,11 @@ struct GroupedPlan {
     size_t counter_bytes_per_problem;
     size_t partial_bytes_per_problem;  // for kGroupRows rows
 };
-GroupedPlan plan_grouped(int inputs, int outputs, int max_bits, int problems, int sm_count);
+// `problems` = the number of problems a launch is EXPECTED to have live (it sets the partition
+// count).  `headroom` sizes the scratch for that many times the planned partitions, so that
+// replan_grouped may choose more of them later, when the expectation changes.
+GroupedPlan plan_grouped(int inputs, int outputs, int max_bits, int problems, int sm_count, int headroom = 1);
+GroupedPlan replan_grouped(const GroupedPlan& sized, int inputs, int outputs, int max_bits, int problems, int sm_count);
 // `problems` lives in device memory; slots with rows == 0 are skipped on the device.
 cudaError_t launch_grouped(const GroupedProblem* problems, int problem_count, int inputs, int outputs,
                            int codebook, const GroupedPlan& plan, unsigned int* status, bool programmatic,

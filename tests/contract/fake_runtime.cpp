@@ -148,9 +148,10 @@ cudaError_t launch_gemm(const LinearCall& call, const GemmPlan&, void* workspace
     record().last = call; record().last_workspace = workspace; record().last_stream = stream; record().last_was_gemm = true;
     return mock::launched();
 }
-GroupedPlan plan_grouped(int, int outputs, int, int, int) {
+GroupedPlan replan_grouped(const GroupedPlan& sized, int, int, int, int, int) { return sized; }
+GroupedPlan plan_grouped(int, int outputs, int, int, int, int) {
     GroupedPlan p{};
-    p.splits = 2; p.stages = 2; p.ctas_per_problem = 2;
+    p.splits = 2; p.scratch_splits = 2; p.stages = 2; p.ctas_per_problem = 2;
     p.counter_bytes_per_problem = align_up((size_t)outputs / 128 * 4);
     p.partial_bytes_per_problem = align_up((size_t)outputs * 2 * kGroupRows * 4);
     return p;
