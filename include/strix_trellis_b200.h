@@ -117,7 +117,9 @@ strix_status strix_b200_moe_combine_rows(strix_context context, const float *row
  * sum over its own experts' slots, the reference's per-rank semantics,
  * include/strix_trellis.h:215-216); the default window is the whole bank.  Every rank applies
  * the same row rules (ids in range and distinct, scores finite and non-negative), so all ranks
- * agree on which rows are valid.  No counterpart as an entry point in the reference. */
+ * agree on which rows are valid.  The call also re-plans how finely the grouped launches cut K,
+ * for the routes this rank expects to own (all routes x bank / experts_total), within the
+ * scratch the plan was created with.  No counterpart as an entry point in the reference. */
 strix_status strix_b200_moe_plan_set_window(strix_tp_moe_plan plan, uint32_t first_expert,
                                             uint32_t experts_total);
 /* Routing, gate/up, SwiGLU and down projections of the routes this rank owns, without the
