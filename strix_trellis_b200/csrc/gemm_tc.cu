@@ -90,6 +90,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
     const int splits = args.k_splits;
     const int tiles = args.n_pairs * args.m_pairs * splits;
     const int my_tiles = tiles > (int)blockIdx.x ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    // accumulators (128-row halves) of row tile mp that hold any of the call's rows: the last row
+    // tile of a call may need only the first, and then nothing is loaded, multiplied or read back
+    // for the second
+    auto live_mt = [&](int mp) {
+        const int left = c.rows - mp * (kBM * kMT);
+        return left > kBM ? kMT : 1;
+    };
     auto k_begin_of = [&](int t) { return kt64 * (t % splits) / splits; };
     auto k_end_of = [&](int t) { return kt64 * (t % splits + 1) / splits; };
 
@@ -127,6 +134,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
             for (int lt = 0; lt < my_tiles && !s_abort; ++lt) {
                 const int t = (int)blockIdx.x + lt * (int)gridDim.x;
                 const int mp = (t / splits) % args.m_pairs;
+                const int live = live_mt(mp);
                 for (int ks = k_begin_of(t), ke = k_end_of(t); ks < ke; ++ks, ++it) {
                     const int st = it % kStagesTc;
                     if (it >= kStagesTc &&
@@ -135,9 +143,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                         break;
                     }
                     unsigned char* dst = ring + (size_t)st * kStageBytesTc;
-                    mbar_expect_tx(full + 8 * st, kMT * kTileBytes);
-#pragma unroll
-                    for (int mt = 0; mt < kMT; ++mt)
+                    mbar_expect_tx(full + 8 * st, live * kTileBytes);
+                    for (int mt = 0; mt < live; ++mt)
                         bulk_load(smem_u32(dst + mt * kTileBytes),
                                   args.a_tiles + ((size_t)(mp * kMT + mt) * kt64 + ks) * kTileBytes, kTileBytes,
                                   full + 8 * st);
@@ -160,6 +167,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                 tc_fence_after_sync();
                 const int t = (int)blockIdx.x + lt * (int)gridDim.x;
                 const int kb = k_begin_of(t);
+                const int live = live_mt((t / splits) % args.m_pairs);
                 for (int ks = kb, ke = k_end_of(t); ks < ke && !s_abort; ++ks, ++it) {
                     const int st = it % kStagesTc;
                     const uint32_t par = (uint32_t)(it / kStagesTc) & 1;
@@ -170,8 +178,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                     tc_fence_after_sync();
                     const uint32_t base = smem_u32(ring + (size_t)st * kStageBytesTc);
                     const uint64_t bdesc = umma_desc_k_major_sw128(base + kMT * kTileBytes);
-#pragma unroll
-                    for (int mt = 0; mt < kMT; ++mt) {
+                    for (int mt = 0; mt < live; ++mt) {
                         const uint64_t adesc = umma_desc_k_major_sw128(base + mt * kTileBytes);
 #pragma unroll
                         for (int k4 = 0; k4 < kBK / 16; ++k4)  // +32 bytes per 16-element K step
@@ -197,7 +204,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                 break;
             }
             tc_fence_after_sync();
-            for (int mt = 0; mt < kMT; ++mt) {
+            for (int mt = 0; mt < live_mt(mp); ++mt) {
                 for (int cb = 0; cb < kBN / 128; ++cb) {
                     const int nb = np * (kBN / 128) + cb;
                     if (nb >= nblocks) continue;  // odd column-block count: second half is padding
