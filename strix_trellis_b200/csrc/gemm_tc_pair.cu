@@ -9,8 +9,8 @@
 // Per CTA: warp 0 activation producer (bulk copies), warp 1 MMA issuer (leader CTA) or relay
 // (partner CTA: ONE remote arrival per stage once its activation tiles have landed and its
 // decoders are done), warps 2-9 epilogue of the CTA's own accumulators (two per tensor-memory
-// lane quarter, one per 128-column block), warps 10-25 decoders (column tile = d % 8,
-// K half = d / 8).  Barriers another CTA arrives on are waited with cluster scope; a
+// lane quarter), warps 10-25 decoders (column tile = d % 8, K half = d / 8); on a CTA's last
+// tile the decoders, idle by then, take a share of the epilogue with staging areas in the ring.  Barriers another CTA arrives on are waited with cluster scope; a
 // tcgen05.commit arrives on both CTAs' barriers at once.  Every wait is bounded and reports
 // into the status word; both CTAs meet at a cluster barrier before tensor memory is returned.
 #include "backend.h"
@@ -30,6 +30,7 @@ constexpr int kDecodeWarps = 16, kEpiWarps = 8;  // two epilogue warps per tenso
 constexpr int kThreadsP = (2 + kEpiWarps + kDecodeWarps) * 32;
 constexpr int kStagingStride = 129;
 constexpr int kStagingBytes = 16 * kStagingStride * 4;
+static_assert((size_t)kDecodeWarps * kStagingBytes <= (size_t)kStagesP * kStageBytesP, "the decoders' last-tile staging fits the ring");
 constexpr size_t kSmemP = 1024 + (size_t)kStagesP * kStageBytesP + (size_t)kEpiWarps * kStagingBytes + 256;
 constexpr uint32_t kTmemCols = 512;
 
@@ -86,6 +87,61 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
     cluster_sync_all();  // barriers initialised and tensor memory allocated in BOTH CTAs
     tc_fence_after_sync();
     const uint32_t tmem_base = s_tmem_base;
+
+    // One half-item of the epilogue of tile t: 16 rows x 128 columns of one accumulator leave tensor
+    // memory through `stage` (16 x 129 floats of the calling warp), then H128, output signs, bias,
+    // alpha/beta and the stores.  item = accumulator * 4 + column block * 2 + half.  (As a separate
+    // device function it cost a third of the kernel's speed: a call gives the whole kernel a stack frame.)
+    auto epilogue_half = [&](int t, int item, int quarter, float* stage) {
+        const int np = t / args.m_quads, mq = t % args.m_quads;
+        const int mt = item >> 2, cb = (item >> 1) & 1, half = item & 1;
+        const int nb = np * (kBN / 128) + cb;
+        if (nb >= nblocks) return;  // odd column-block count: second half is padding
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + mt * kBN + cb * 128;
+        float sv[4], bi[4];
+    #pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int cidx = nb * 128 + lane + 32 * j;
+            sv[j] = half_bits_to_float(c.w.svh[cidx]);
+            bi[j] = c.w.bias ? c.w.bias[cidx] : 0.f;
+        }
+    #pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + ch * 32, r);
+            tmem_ld_wait();
+            if ((lane >> 4) == half) {
+    #pragma unroll
+                for (int j = 0; j < 32; ++j) stage[(lane & 15) * kStagingStride + ch * 32 + j] = __uint_as_float(r[j]);
+            }
+        }
+        __syncwarp();
+        const int row_base = ((mq * 4 + (int)rank * 2 + mt) * kBM) + quarter * 32 + half * 16;
+        for (int r4 = 0; r4 < 16; r4 += 4) {
+            float v[4][4];
+    #pragma unroll
+            for (int u = 0; u < 4; ++u)
+    #pragma unroll
+                for (int j = 0; j < 4; ++j) v[u][j] = stage[(r4 + u) * kStagingStride + lane + 32 * j];
+    #pragma unroll
+            for (int u = 0; u < 4; ++u) hadamard128_warp(v[u], lane);
+    #pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int row = row_base + r4 + u;
+                if (row < c.rows) {
+                    const long long out = (long long)row * c.y_stride + nb * 128 + lane;
+    #pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float value = __fmul_rn(v[u][j], sv[j]);
+                        if (c.w.bias) value = __fadd_rn(value, bi[j]);
+                        scale_and_store(c.y, c.y_dtype, out + 32 * j, value, c.alpha, c.beta);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    };
+
 
     if (warp == 0) {
         // ---- activation producer: this CTA's two 128-row tiles of every K step -------------
@@ -164,72 +220,28 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
         }
     } else if (warp < 2 + kEpiWarps) {
         // ---- epilogue of this CTA's 256 rows --------------------------------------------------
-        const int quarter = warp & 3;
+        // A lane quarter's work on a tile is eight half-items (accumulator, column block, 16-row
+        // half).  On every tile but the last its two epilogue warps take four each; on a CTA's
+        // LAST tile the four decoder warps of the quarter, idle by then, take a share too.
+        const int quarter = warp & 3, mine = (warp - 2) >> 2;
         float* stage = staging + (size_t)(warp - 2) * 16 * kStagingStride;
         const uint32_t leader_tmem_empty = map_to_rank(tmem_empty, 0);
         for (int lt = 0; lt < my_tiles; ++lt) {
             const int t = pair + lt * pairs;
-            const int np = t / args.m_quads, mq = t % args.m_quads;
             if (s_abort || !mbar_wait_cluster(tmem_full, (uint32_t)lt & 1, c.status, kTimeoutTensorPipe)) {
                 s_abort = 1;
                 break;
             }
             tc_fence_after_sync();
-            for (int mt = 0; mt < kMT; ++mt) {
-                for (int cb = (warp - 2) >> 2; cb < kBN / 128; cb += kEpiWarps / 4) {  // this warp's column block(s)
-                    const int nb = np * (kBN / 128) + cb;
-                    if (nb >= nblocks) continue;  // odd column-block count: second half is padding
-                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + mt * kBN + cb * 128;
-                    float sv[4], bi[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int cidx = nb * 128 + lane + 32 * j;
-                        sv[j] = half_bits_to_float(c.w.svh[cidx]);
-                        bi[j] = c.w.bias ? c.w.bias[cidx] : 0.f;
-                    }
-                    for (int half = 0; half < 2; ++half) {
-#pragma unroll
-                        for (int ch = 0; ch < 4; ++ch) {
-                            uint32_t r[32];
-                            tmem_ld_32x32(taddr + ch * 32, r);
-                            tmem_ld_wait();
-                            if ((lane >> 4) == half) {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    stage[(lane & 15) * kStagingStride + ch * 32 + j] = __uint_as_float(r[j]);
-                            }
-                        }
-                        __syncwarp();
-                        const int row_base = ((mq * 4 + (int)rank * 2 + mt) * kBM) + quarter * 32 + half * 16;
-                        for (int r4 = 0; r4 < 16; r4 += 4) {
-                            float v[4][4];
-#pragma unroll
-                            for (int u = 0; u < 4; ++u)
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) v[u][j] = stage[(r4 + u) * kStagingStride + lane + 32 * j];
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) hadamard128_warp(v[u], lane);
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) {
-                                const int row = row_base + r4 + u;
-                                if (row < c.rows) {
-                                    const long long out = (long long)row * c.y_stride + nb * 128 + lane;
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) {
-                                        float value = __fmul_rn(v[u][j], sv[j]);
-                                        if (c.w.bias) value = __fadd_rn(value, bi[j]);
-                                        scale_and_store(c.y, c.y_dtype, out + 32 * j, value, c.alpha, c.beta);
-                                    }
-                                }
-                            }
-                        }
-                        __syncwarp();
-                    }
-                }
+            if (lt + 1 < my_tiles) {
+                for (int item = mine; item < 8; item += 2) epilogue_half(t, item, quarter, stage);
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(leader_tmem_empty);  // the leader's MMA warp owns the next tile
+            } else {
+                for (int item = mine; item < 8; item += 6) epilogue_half(t, item, quarter, stage);
+                tc_fence_before_sync();
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_tmem_empty);  // the leader's MMA warp owns the next tile
         }
     } else {
         // ---- decoders: this CTA's 128 columns of the stage, swizzled K-major ---------------------
@@ -288,6 +300,17 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
             for (int k2 = 0; k2 < 2; ++k2)
 #pragma unroll
                 for (int j = 0; j < 3; ++j) { w0[k2][j] = w1[k2][j]; w1[k2][j] = w2[k2][j]; }
+        }
+        // The CTA's last tile: the ring is idle for good once its MMAs have completed (every copy
+        // has landed, both CTAs' reads are done), so this warp takes a staging area there and a
+        // share of its lane quarter's epilogue.
+        if (my_tiles > 0 && !s_abort &&
+            mbar_wait_cluster(tmem_full, (uint32_t)(my_tiles - 1) & 1, c.status, kTimeoutTensorPipe)) {
+            tc_fence_after_sync();
+            float* stage = reinterpret_cast<float*>(ring) + (size_t)d * 16 * kStagingStride;
+            const int t = pair + (my_tiles - 1) * pairs;
+            for (int item = 2 + (d >> 2); item < 8; item += 6) epilogue_half(t, item, warp & 3, stage);
+            tc_fence_before_sync();
         }
     }
 
