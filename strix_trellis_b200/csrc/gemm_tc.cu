@@ -37,6 +37,8 @@ constexpr int kStagingStride = 129;                            // floats per sta
 constexpr int kStagingBytes = 16 * kStagingStride * 4;         // per epilogue warp, 16 rows at a time
 constexpr size_t kSmemTc = 1024 + (size_t)kStagesTc * kStageBytesTc + (size_t)kEpiWarps * kStagingBytes + 128;
 constexpr uint32_t kTmemCols = 512;
+static_assert((size_t)kDecodeWarps * kStagingBytes <= (size_t)kStagesTc * kStageBytesTc,
+              "the decoder warps' staging areas of the last work item must fit the idle ring");
 
 struct GemmArgs {
     LinearCall call;
@@ -127,6 +129,72 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
     tc_fence_after_sync();
     const uint32_t tmem_base = s_tmem_base;
 
+    // One half-item of the epilogue of work item t: 16 rows x 128 columns of one accumulator leave
+    // tensor memory through `stage` (16 x 129 floats of the calling warp); a K partition stores
+    // them raw for splitk_finish_kernel, a whole tile gets H128, output signs, bias, alpha/beta.
+    // item = accumulator * 4 + column block * 2 + half.
+    auto epilogue_half = [&](int t, int item, int quarter, float* stage) {
+        const int np = (t / splits) / args.m_pairs, mp = (t / splits) % args.m_pairs;
+        const int mt = item >> 2, cb = (item >> 1) & 1, half = item & 1;
+        const int nb = np * (kBN / 128) + cb;
+        if (mt >= live_mt(mp) || nb >= nblocks) return;  // no rows of the call / padding column block
+        float* raw = splits > 1 ? args.partials + (size_t)(t % splits) * args.m_pairs * (kBM * kMT) * c.w.outputs : nullptr;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + mt * kBN + cb * 128;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + ch * 32, r);
+            tmem_ld_wait();
+            if ((lane >> 4) == half) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) stage[(lane & 15) * kStagingStride + ch * 32 + j] = __uint_as_float(r[j]);
+            }
+        }
+        __syncwarp();
+        const int row_base = (mp * kMT + mt) * kBM + quarter * 32 + half * 16;
+        if (raw) {
+            for (int r1 = 0; r1 < 16; ++r1) {
+                const int row = row_base + r1;
+                if (row < c.rows) {
+                    float* out = raw + (size_t)row * c.w.outputs + nb * 128 + lane;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) out[32 * j] = stage[r1 * kStagingStride + lane + 32 * j];
+                }
+            }
+        } else {
+            float sv[4], bi[4];  // per-column constants of this lane's four columns
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int cidx = nb * 128 + lane + 32 * j;
+                sv[j] = half_bits_to_float(c.w.svh[cidx]);
+                bi[j] = c.w.bias ? c.w.bias[cidx] : 0.f;
+            }
+            for (int r4 = 0; r4 < 16; r4 += 4) {  // four independent rows in flight
+                float v[4][4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[u][j] = stage[(r4 + u) * kStagingStride + lane + 32 * j];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) hadamard128_warp(v[u], lane);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int row = row_base + r4 + u;
+                    if (row < c.rows) {
+                        const long long out = (long long)row * c.y_stride + nb * 128 + lane;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float value = __fmul_rn(v[u][j], sv[j]);
+                            if (c.w.bias) value = __fadd_rn(value, bi[j]);
+                            scale_and_store(c.y, c.y_dtype, out + 32 * j, value, c.alpha, c.beta);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    };
+
     if (warp == 0) {
         // ---- A producer ---------------------------------------------------------------
         if (lane == 0) {
@@ -191,86 +259,28 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
         }
     } else if (warp < 2 + kEpiWarps) {
         // ---- epilogue -------------------------------------------------------------------
+        // A lane quarter's work on a tile is eight half-items (accumulator, column block, 16-row
+        // half): its one epilogue warp takes them all, except on the CTA's LAST work item, where
+        // the four decoder warps of the quarter, idle by then, take a share.
         const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. +31
         float* stage = staging + (size_t)(warp - 2) * 16 * kStagingStride;
         for (int lt = 0; lt < my_tiles; ++lt) {
             const int t = (int)blockIdx.x + lt * (int)gridDim.x;
-            const int np = (t / splits) / args.m_pairs, mp = (t / splits) % args.m_pairs;
-            // K partitions leave raw accumulators; splitk_finish_kernel folds and finishes them
-            float* raw = splits > 1 ? args.partials + (size_t)(t % splits) * args.m_pairs * (kBM * kMT) * c.w.outputs
-                                    : nullptr;
             if (s_abort || !mbar_wait(tmem_full, (uint32_t)lt & 1, c.status, kTimeoutTensorPipe)) {
                 s_abort = 1;
                 break;
             }
             tc_fence_after_sync();
-            for (int mt = 0; mt < live_mt(mp); ++mt) {
-                for (int cb = 0; cb < kBN / 128; ++cb) {
-                    const int nb = np * (kBN / 128) + cb;
-                    if (nb >= nblocks) continue;  // odd column-block count: second half is padding
-                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + mt * kBN + cb * 128;
-                    // per-column constants of this lane's four columns, loaded once per block
-                    float sv[4], bi[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int cidx = nb * 128 + lane + 32 * j;
-                        sv[j] = half_bits_to_float(c.w.svh[cidx]);
-                        bi[j] = c.w.bias ? c.w.bias[cidx] : 0.f;
-                    }
-                    for (int half = 0; half < 2; ++half) {  // lanes [16*half, +16) stage their rows
-#pragma unroll
-                        for (int ch = 0; ch < 4; ++ch) {
-                            uint32_t r[32];
-                            tmem_ld_32x32(taddr + ch * 32, r);
-                            tmem_ld_wait();
-                            if ((lane >> 4) == half) {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    stage[(lane & 15) * kStagingStride + ch * 32 + j] = __uint_as_float(r[j]);
-                            }
-                        }
-                        __syncwarp();
-                        const int row_base = (mp * kMT + mt) * kBM + quarter * 32 + half * 16;
-                        if (raw) {
-                            for (int r1 = 0; r1 < 16; ++r1) {
-                                const int row = row_base + r1;
-                                if (row < c.rows) {
-                                    float* out = raw + (size_t)row * c.w.outputs + nb * 128 + lane;
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) out[32 * j] = stage[r1 * kStagingStride + lane + 32 * j];
-                                }
-                            }
-                        } else
-                        for (int r4 = 0; r4 < 16; r4 += 4) {  // four independent rows in flight
-                            float v[4][4];
-#pragma unroll
-                            for (int u = 0; u < 4; ++u)
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) v[u][j] = stage[(r4 + u) * kStagingStride + lane + 32 * j];
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) hadamard128_warp(v[u], lane);
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) {
-                                const int row = row_base + r4 + u;
-                                if (row < c.rows) {
-                                    const long long out = (long long)row * c.y_stride + nb * 128 + lane;
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) {
-                                        float value = __fmul_rn(v[u][j], sv[j]);
-                                        if (c.w.bias) value = __fadd_rn(value, bi[j]);
-                                        scale_and_store(c.y, c.y_dtype, out + 32 * j, value, c.alpha, c.beta);
-                                    }
-                                }
-                            }
-                        }
-                        __syncwarp();
-                    }
-                }
+            if (lt + 1 < my_tiles) {
+                for (int item = 0; item < 8; ++item) epilogue_half(t, item, quarter, stage);
+                // all four accumulators read: hand tensor memory back to the MMA warp
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty);
+            } else {
+                for (int item = 0; item < 8; item += 5) epilogue_half(t, item, quarter, stage);
+                tc_fence_before_sync();
             }
-            // all four accumulators read: hand tensor memory back to the MMA warp
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty);
         }
     } else {
         // ---- decoders: trellis tiles -> swizzled K-major B stage -------------------------------
@@ -339,6 +349,15 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
             for (int k4 = 0; k4 < 4; ++k4)
 #pragma unroll
                 for (int j = 0; j < 3; ++j) cur[k4][j] = nxt[k4][j];
+        }
+        // The CTA's last work item: the ring is idle for good once its MMAs have completed, so
+        // this warp takes a staging area there and a share of its lane quarter's epilogue.
+        if (my_tiles > 0 && !s_abort && mbar_wait(tmem_full, (uint32_t)(my_tiles - 1) & 1, c.status, kTimeoutTensorPipe)) {
+            tc_fence_after_sync();
+            float* stage = reinterpret_cast<float*>(ring) + (size_t)d * 16 * kStagingStride;
+            const int t = (int)blockIdx.x + (my_tiles - 1) * (int)gridDim.x;
+            for (int item = 1 + (d >> 2); item < 8; item += 5) epilogue_half(t, item, warp & 3, stage);
+            tc_fence_before_sync();
         }
     }
 
