@@ -37,6 +37,8 @@ constexpr int kStagingStride = 129;                            // floats per sta
 constexpr int kStagingBytes = 16 * kStagingStride * 4;         // per epilogue warp, 16 rows at a time
 constexpr size_t kSmemTc = 1024 + (size_t)kStagesTc * kStageBytesTc + (size_t)kEpiWarps * kStagingBytes + 128;
 constexpr uint32_t kTmemCols = 512;
+constexpr int kChunkedMaxRows = 16;  // more rows than this take the tensor-core route
+constexpr int kWeightsAhead = 8;  // K steps between the L2 prefetch of weight words and their use
 static_assert((size_t)kDecodeWarps * kStagingBytes <= (size_t)kStagesTc * kStageBytesTc,
               "the decoder warps' staging areas of the last work item must fit the idle ring");
 
@@ -57,6 +59,7 @@ __global__ void input_tiles_kernel(const float* __restrict__ x, int x_dtype, lon
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = inputs / 128, kt64 = inputs / 64;
     const long long groups = (long long)rows_padded * blocks_per_row;
+    pdl_launch_dependents();  // the GEMM may set itself up and decode its first weights meanwhile
     for (long long g = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5); g < groups;
          g += (long long)gridDim.x * (blockDim.x >> 5)) {
         const int row = (int)(g / blocks_per_row), blk = (int)(g % blocks_per_row);
@@ -128,6 +131,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = s_tmem_base;
+    pdl_launch_dependents();
 
     // One half-item of the epilogue of work item t: 16 rows x 128 columns of one accumulator leave
     // tensor memory through `stage` (16 x 129 floats of the calling warp); a K partition stores
@@ -198,6 +202,36 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
     if (warp == 0) {
         // ---- A producer ---------------------------------------------------------------
         if (lane == 0) {
+            // The decoders read their words straight from global memory, one K step ahead: with
+            // weights that no other CTA has touched that is a DRAM round trip per K step.  This
+            // thread asks the L2 for the CTA's words kWeightsAhead K steps before they are read
+            // (a K step of one 128-column block is one contiguous run of the stream).
+            constexpr uint32_t kStepBytes = 4 * 8 * tile_words(K) * 4;
+            int plt = -1, pks = 0, pke = 0;
+            const unsigned char* pbase[kBN / 128] = {};
+            auto prefetch_step = [&]() {
+                while (pks == pke) {  // next work item of this CTA
+                    if (++plt >= my_tiles) return;
+                    const int t = (int)blockIdx.x + plt * (int)gridDim.x;
+                    pks = k_begin_of(t);
+                    pke = k_end_of(t);
+                    for (int cb = 0; cb < kBN / 128; ++cb) {
+                        const int nb = ((t / splits) / args.m_pairs) * (kBN / 128) + cb;
+                        pbase[cb] = nb < nblocks ? reinterpret_cast<const unsigned char*>(
+                                                       c.w.packed + (size_t)nb * ktiles16 * 8 * tile_words(K))
+                                                 : nullptr;
+                    }
+                }
+                for (int cb = 0; cb < kBN / 128; ++cb)
+                    if (pbase[cb]) bulk_prefetch_l2(pbase[cb] + (size_t)pks * kStepBytes, kStepBytes);
+                ++pks;
+            };
+            for (int i = 0; i < kWeightsAhead; ++i) prefetch_step();
+            // Launched programmatically after input_tiles_kernel: everything up to here, and the
+            // decoders' first stages (weights are immutable), overlap its tail; only the
+            // activation tiles need its memory.  Everything older than that kernel was complete
+            // before it started.
+            pdl_wait_prior_grid();
             int it = 0;
             for (int lt = 0; lt < my_tiles && !s_abort; ++lt) {
                 const int t = (int)blockIdx.x + lt * (int)gridDim.x;
@@ -216,6 +250,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
                         bulk_load(smem_u32(dst + mt * kTileBytes),
                                   args.a_tiles + ((size_t)(mp * kMT + mt) * kt64 + ks) * kTileBytes, kTileBytes,
                                   full + 8 * st);
+                    prefetch_step();
                 }
             }
             // Never leave with a copy still landing in this CTA's shared memory.
@@ -318,11 +353,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
             ++fks;
             ++fetched;
         };
-        uint32_t cur[4][3] = {}, nxt[4][3] = {};
+        uint32_t cur[4][3] = {}, nxt[4][3] = {}, far[4][3] = {};  // this K step and the next two, in flight
         if (iters > 0) fetch(cur);
+        if (iters > 1) fetch(nxt);
         for (int it = 0; it < iters && !s_abort; ++it) {
             const int st = it % kStagesTc;
-            if (fetched < iters) fetch(nxt);  // in flight while this stage is decoded
+            if (fetched < iters) fetch(far);  // two K steps ahead: one decode time does not cover an L2 round trip
             if (it >= kStagesTc &&
                 !mbar_wait(empty + 8 * st, (uint32_t)((it / kStagesTc) - 1) & 1, c.status, kTimeoutTensorPipe)) {
                 s_abort = 1;
@@ -348,7 +384,10 @@ __global__ void __launch_bounds__(kThreadsTc, 1) gemm_tc_kernel(const GemmArgs a
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4)
 #pragma unroll
-                for (int j = 0; j < 3; ++j) cur[k4][j] = nxt[k4][j];
+                for (int j = 0; j < 3; ++j) {
+                    cur[k4][j] = nxt[k4][j];
+                    nxt[k4][j] = far[k4][j];
+                }
         }
         // The CTA's last work item: the ring is idle for good once its MMAs have completed, so
         // this warp takes a staging area there and a share of its lane quarter's epilogue.
@@ -379,6 +418,7 @@ __global__ void splitk_finish_kernel(const float* __restrict__ partials, int spl
     const int lane = threadIdx.x & 31;
     const int nblocks = outputs / 128;
     const long long items = (long long)rows * nblocks;
+    pdl_wait_prior_grid();  // the partial accumulators belong to the GEMM before this launch
     for (long long g = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5); g < items;
          g += (long long)gridDim.x * (blockDim.x >> 5)) {
         const int row = (int)(g / nblocks), nb = (int)(g % nblocks);
@@ -409,7 +449,11 @@ int gemm_pair_rows_padded(int rows);
 cudaError_t launch_gemm_pair(const LinearCall& call, const unsigned char* a_tiles, int sm_count, cudaStream_t stream);
 
 GemmPlan plan_gemm(const DeviceWeights& w, int rows, int sm_count) {
-    if (rows < 64) return plan_gemm_chunked(w, rows, sm_count);
+    // Up to two 8-row chunks of the fused GEMV are faster than the three launches of the
+    // tensor-core route (measured on cold weights, K4: 4096 -> 12288 45 against 39 us at 16 rows,
+    // but 4096 -> 4096 23 against 31 and 14336 -> 4096 52 against 74); from 17 rows on the
+    // tensor-core route wins or ties on every benchmark shape.
+    if (rows <= kChunkedMaxRows) return plan_gemm_chunked(w, rows, sm_count);
     GemmPlan plan{};
     const bool pair = rows > kBM * kMT && sm_count >= 2;
     const int rows_padded = pair ? gemm_pair_rows_padded(rows) : (rows + kBM * kMT - 1) / (kBM * kMT) * (kBM * kMT);
@@ -435,9 +479,18 @@ GemmPlan plan_gemm(const DeviceWeights& w, int rows, int sm_count) {
 }
 
 template <int K, int CB>
-static cudaError_t launch_tc(const GemmArgs& args, int grid, cudaStream_t stream) {
-    gemm_tc_kernel<K, CB><<<grid, kThreadsTc, kSmemTc, stream>>>(args);
-    return cudaGetLastError();
+static cudaError_t launch_tc(const GemmArgs& args, int grid, bool programmatic, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreadsTc);
+    cfg.dynamicSmemBytes = kSmemTc;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<K, CB>, args);
 }
 
 // Opt-in dynamic shared memory is a per-device function attribute: set for every instantiation
@@ -468,21 +521,21 @@ cudaError_t configure_gemm_tc_kernels() {
 }
 
 template <int CB>
-static cudaError_t launch_tc_bits(const GemmArgs& a, int grid, cudaStream_t s) {
+static cudaError_t launch_tc_bits(const GemmArgs& a, int grid, bool programmatic, cudaStream_t s) {
     switch (a.call.w.bits) {
-    case 1: return launch_tc<1, CB>(a, grid, s);
-    case 2: return launch_tc<2, CB>(a, grid, s);
-    case 3: return launch_tc<3, CB>(a, grid, s);
-    case 4: return launch_tc<4, CB>(a, grid, s);
-    case 5: return launch_tc<5, CB>(a, grid, s);
-    case 6: return launch_tc<6, CB>(a, grid, s);
-    case 7: return launch_tc<7, CB>(a, grid, s);
-    case 8: return launch_tc<8, CB>(a, grid, s);
+    case 1: return launch_tc<1, CB>(a, grid, programmatic, s);
+    case 2: return launch_tc<2, CB>(a, grid, programmatic, s);
+    case 3: return launch_tc<3, CB>(a, grid, programmatic, s);
+    case 4: return launch_tc<4, CB>(a, grid, programmatic, s);
+    case 5: return launch_tc<5, CB>(a, grid, programmatic, s);
+    case 6: return launch_tc<6, CB>(a, grid, programmatic, s);
+    case 7: return launch_tc<7, CB>(a, grid, programmatic, s);
+    case 8: return launch_tc<8, CB>(a, grid, programmatic, s);
     case 9: case 10: case 11:  // 1.5 / 2.5 / 3.5 bits per weight exist for mul1 only
         if constexpr (CB == CB_MUL1) {
-            if (a.call.w.bits == 9) return launch_tc<9, CB>(a, grid, s);
-            if (a.call.w.bits == 10) return launch_tc<10, CB>(a, grid, s);
-            return launch_tc<11, CB>(a, grid, s);
+            if (a.call.w.bits == 9) return launch_tc<9, CB>(a, grid, programmatic, s);
+            if (a.call.w.bits == 10) return launch_tc<10, CB>(a, grid, programmatic, s);
+            return launch_tc<11, CB>(a, grid, programmatic, s);
         }
         return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
@@ -491,7 +544,9 @@ static cudaError_t launch_tc_bits(const GemmArgs& a, int grid, cudaStream_t s) {
 
 cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* workspace, bool programmatic_launch,
                         cudaStream_t stream) {
-    // Only the 8-row chunks launch programmatically; the tensor-core kernels are ordinary launches.
+    // The 8-row chunks launch programmatically after whatever precedes them in the stream.  The
+    // tensor-core route starts with an ordinary launch (input_tiles_kernel) and chains its own
+    // later launches to it programmatically.
     if (!plan.tensor_core) return launch_gemm_chunked(call, plan.sm_count, workspace, programmatic_launch, stream);
     if (!workspace) return cudaErrorInvalidValue;
     const bool pair = plan.tile_m == 2 * kBM * kMT;
@@ -519,18 +574,26 @@ cudaError_t launch_gemm(const LinearCall& call, const GemmPlan& plan, void* work
     const int grid = (int)(tiles < plan.sm_count ? tiles : plan.sm_count);
     cudaError_t e;
     switch (call.w.codebook) {
-    case CB_3INST: e = launch_tc_bits<CB_3INST>(args, grid, stream); break;
-    case CB_MCG: e = launch_tc_bits<CB_MCG>(args, grid, stream); break;
-    case CB_MUL1: e = launch_tc_bits<CB_MUL1>(args, grid, stream); break;
+    case CB_3INST: e = launch_tc_bits<CB_3INST>(args, grid, programmatic_launch, stream); break;
+    case CB_MCG: e = launch_tc_bits<CB_MCG>(args, grid, programmatic_launch, stream); break;
+    case CB_MUL1: e = launch_tc_bits<CB_MUL1>(args, grid, programmatic_launch, stream); break;
     default: return cudaErrorInvalidValue;
     }
     if (e != cudaSuccess || plan.k_splits == 1) return e;
     const long long items = (long long)call.rows * (call.w.outputs / 128);
     const long long want = (items + 7) / 8;
-    splitk_finish_kernel<<<streaming_grid(want), 256, 0, stream>>>(
-        args.partials, plan.k_splits, (size_t)rows_padded * call.w.outputs, call.rows, call.w.outputs, call.w.svh,
-        call.w.bias, call.alpha, call.beta, call.y, call.y_dtype, call.y_stride);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(streaming_grid(want));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic_launch ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, splitk_finish_kernel, (const float*)args.partials, plan.k_splits,
+                              (size_t)rows_padded * call.w.outputs, call.rows, call.w.outputs, call.w.svh, call.w.bias,
+                              call.alpha, call.beta, call.y, call.y_dtype, call.y_stride);
 }
 
 }  // namespace st

@@ -33,6 +33,7 @@ constexpr int kStagingBytes = 16 * kStagingStride * 4;
 static_assert((size_t)kDecodeWarps * kStagingBytes <= (size_t)kStagesP * kStageBytesP, "the decoders' last-tile staging fits the ring");
 constexpr size_t kSmemP = 1024 + (size_t)kStagesP * kStageBytesP + (size_t)kEpiWarps * kStagingBytes + 256;
 constexpr uint32_t kTmemCols = 512;
+constexpr int kWeightsAhead = 8;  // K steps between the L2 prefetch of weight words and their use
 
 struct PairArgs {
     LinearCall call;
@@ -146,6 +147,24 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
     if (warp == 0) {
         // ---- activation producer: this CTA's two 128-row tiles of every K step -------------
         if (lane == 0) {
+            // L2 prefetch of this CTA's weight words kWeightsAhead K steps before its decoders
+            // read them (a K step of a 128-column block is one contiguous run of the stream).
+            constexpr uint32_t kStepBytes = 4 * 8 * tile_words(K) * 4;
+            int plt = -1, pks = kt64;
+            const unsigned char* pbase = nullptr;
+            auto prefetch_step = [&]() {
+                if (pks == kt64) {  // next tile of this pair
+                    if (++plt >= my_tiles) { --plt; return; }
+                    const int nb = ((pair + plt * pairs) / args.m_quads) * (kBN / 128) + (int)rank;
+                    pbase = nb < nblocks ? reinterpret_cast<const unsigned char*>(
+                                               c.w.packed + (size_t)nb * ktiles16 * 8 * tile_words(K))
+                                         : nullptr;
+                    pks = 0;
+                }
+                if (pbase) bulk_prefetch_l2(pbase + (size_t)pks * kStepBytes, kStepBytes);
+                ++pks;
+            };
+            for (int i = 0; i < kWeightsAhead; ++i) prefetch_step();
             int it = 0;
             for (int lt = 0; lt < my_tiles && !s_abort; ++lt) {
                 const int t = pair + lt * pairs;
@@ -164,6 +183,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) gemm_tc_pair_kernel(const PairAr
                         bulk_load(smem_u32(dst + mt * kTileBytes),
                                   args.a_tiles + ((size_t)(mq * 4 + (int)rank * 2 + mt) * kt64 + ks) * kTileBytes,
                                   kTileBytes, a_bar + 8 * st);
+                    prefetch_step();
                 }
             }
             for (int i = (it > kStagesP ? it - kStagesP : 0); i < it; ++i)  // nothing still landing at exit

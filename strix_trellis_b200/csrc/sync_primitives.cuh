@@ -89,6 +89,11 @@ __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, ui
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// Asks the L2 to fetch `bytes` (a multiple of 16) at the 16-byte aligned `src`; nothing waits
+// for it and nothing depends on it.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 // Programmatic dependent launch: let the next grid of the stream start its
 // independent prologue, and wait for the previous grid's memory before touching
 // anything it may have written.  Both are no-ops for an ordinary launch.

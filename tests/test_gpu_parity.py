@@ -232,7 +232,7 @@ def test_half_integer_rates_decode_bit_exact_and_multiply(ctx, golden_dir):
         assert host(w.dequantize()).tobytes() == ref.dequantize(layer.trellis, rate, "mul1").tobytes()
         for rows in (1, 3, 8):
             gate(host(w.gemv(dev(x[:rows]))), want[:rows], f"rate {rate} gemv rows {rows}")
-        for rows in (20, 100):
+        for rows in (12, 20, 100):
             gate(host(w.gemm(dev(x[:rows]))), want[:rows], f"rate {rate} gemm rows {rows}")
         _, _, core_in = w.input_stages(dev(x[:2]))
         exact = w.output_stages(w.core_exact(core_in))
@@ -243,7 +243,7 @@ def test_half_integer_rates_decode_bit_exact_and_multiply(ctx, golden_dir):
         ctx.prepare(synthetic.Layer(t, ones, more_ones, None, 3.5, "mcg"))
 
 
-@pytest.mark.parametrize("rows", [1, 5, 24, 300])
+@pytest.mark.parametrize("rows", [1, 5, 12, 24, 300])
 def test_half_precision_tensors_widen_on_load_and_round_on_store(ctx, rows):
     """binary16 / bfloat16 activations and outputs (reserved and refused by the reference,
     include/strix_trellis.h:39-40; honoured here).  The arithmetic is the float32 contract: an
@@ -304,6 +304,7 @@ def test_config1_against_reference_golden(ctx, golden_dir):
 
 @pytest.mark.parametrize("rows", [9, 16, 17, 32])
 def test_gemm_small_rows(ctx, grid, rows):
+    """Up to 16 rows run as 8-row chunks of the fused GEMV, more rows take the tcgen05 kernel."""
     meta, outs = grid
     for case in meta["cases"][::7]:
         layer, _, _, _ = synthetic.grid_case(case["codebook"], case["bits"], case["wide"], meta["rows"])
@@ -314,9 +315,9 @@ def test_gemm_small_rows(ctx, grid, rows):
         w.close()
 
 
-@pytest.mark.parametrize("rows", [64, 128, 200, 256, 300, 513, 1030])
+@pytest.mark.parametrize("rows", [40, 64, 128, 200, 256, 300, 513, 1030])
 def test_gemm_tensor_core_small_layers(ctx, grid, rows):
-    """Rows >= 64 take the tcgen05 kernel: every rate and codebook, ragged row counts."""
+    """More than 16 rows take the tcgen05 kernels: every rate and codebook, ragged row counts."""
     meta, outs = grid
     for case in meta["cases"][::3]:
         layer, _, _, _ = synthetic.grid_case(case["codebook"], case["bits"], case["wide"], meta["rows"])
