@@ -21,7 +21,7 @@ With N>1 (launched under torchrun) every rank runs the same workload on its own 
 the timed region: rates x rows on the largest shape, the prefill GEMM (K4/K5/K6), the
 routed-expert block on one rank's bank, and at every N the tensor-parallel dense layers
 (row-parallel + all-reduce, LM head + all-gather) and the expert-parallel block
-(all-to-all dispatch and return).  `--no-extra` skips them; `--case gemv|gemm|moe` runs one
+(all-to-all dispatch and return).  `--no-extra` skips them; `--case gemv|gemm|gemm-small|moe|decode` runs one
 small fixed workload of one kernel for profilers.
 
 `--impl reference` times the CPU contract (this repository's C restatement of the
@@ -508,6 +508,9 @@ def run_case(args):
     elif args.case == "gemm":
         print(json.dumps({"case": "gemm 4096->12288 K4", **gemm_case(torch, ctx, stream, [2048], reps=2),
                           "status": ctx.device_status()}))
+    elif args.case == "gemm-small":
+        print(json.dumps({"case": "gemm 4096->12288 K4, one row tile with K partitions",
+                          **gemm_case(torch, ctx, stream, [128], reps=2), "status": ctx.device_status()}))
     else:
         print(json.dumps({"case": "moe bank 32, top-8, 4096/2048 K2", **moe_case(torch, ctx, stream, [8], reps=2),
                           "status": ctx.device_status()}))
@@ -840,7 +843,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the GEMM / MoE / TP side measurements")
-    ap.add_argument("--case", choices=["gemv", "gemm", "moe", "decode"], help="run one small profiling workload and exit")
+    ap.add_argument("--case", choices=["gemv", "gemm", "gemm-small", "moe", "decode"], help="run one small profiling workload and exit")
     args = ap.parse_args()
     if args.case:
         run_case(args)
