@@ -5,16 +5,20 @@
 // input_transform + wmma tiled core + fused output epilogue (src/wmma_tiled.hip:87-269,
 // src/gemm.hip:15-76, src/backend.hip:121-140).
 //
-// Two launches: (1) input stages, writing the RN16 core input as pre-swizzled
+// Launches: (1) input stages, writing the RN16 core input as pre-swizzled
 // [128 rows x 64 k] tiles so that each tile is ONE contiguous 16 KB bulk copy;
-// (2) the persistent GEMM kernel, one CTA per SM.  CTA tile = 256 rows x 256 columns as
+// (2) the persistent GEMM kernel, one CTA per SM, launched programmatically after (1);
+// (3) with one row tile only: K is cut into partitions so that every SM has work, and a
+// finishing kernel folds their raw accumulators.  CTA tile = 256 rows x 256 columns as
 // 2 x (128 x 256) accumulators = all 512 TMEM columns: every decoded weight stage feeds
 // 256 rows and every activation tile feeds 256 columns.  K is stepped by 64.
-//   warp 0      A producer  : cp.async.bulk of the two A tiles of a stage
+//   warp 0      A producer  : cp.async.bulk of the A tiles of a stage; L2 prefetch of the
+//                             CTA's weight words eight K steps ahead
 //   warp 1      MMA issuer  : tcgen05.mma (one thread), tcgen05.commit to the barriers
 //   warps 2-5   epilogue    : tcgen05.ld -> shared staging -> H128 by warp shuffles -> y
-//   warps 6-21  decoders    : one warp per 16-column tile, 4 k-tiles per stage, the next
-//                             stage's ring words prefetched into registers
+//   warps 6-21  decoders    : one warp per 16-column tile, 4 k-tiles per stage, the ring
+//                             words of the next two stages in registers; on the CTA's last
+//                             work item they share the epilogue
 // Every wait is bounded and reports into the device status word.
 #include <cstdlib>
 
