@@ -350,6 +350,21 @@ def test_gemm_tensor_core_prefill_shape(ctx, bits, rows):
     w.close()
 
 
+@pytest.mark.parametrize("rows", [40, 130, 300])
+def test_gemm_more_column_stripes_than_sms(ctx, rows):
+    """A wide, short layer (256 -> 40960: 160 column stripes of 256, four K steps each): with up
+    to 256 rows some CTAs of the single-CTA kernel run two work items, so the weight prefetch and
+    the decoders' look-ahead cross from one item into the next and only the last item's
+    epilogue is shared with the decoder warps; 300 rows take the two-CTA kernel the same way."""
+    layer = synthetic.make_layer(256, 40960, 2, seed=640, bias=True)
+    x = synthetic.make_activations(rows, 256, seed=641)
+    w = ctx.prepare(layer)
+    want = c_oracle.linear(layer.trellis, layer.suh, layer.svh, layer.bias, 2, 2, x)
+    gate(host(w.gemm(dev(x))), want, f"wide layer rows {rows}")
+    assert ctx.device_status() == 0
+    w.close()
+
+
 @pytest.mark.parametrize("bits,rows", [(4, 8192), (4, 2048), (5, 2048), (5, 8192), (6, 2048), (6, 8192)])
 def test_gemm_full_prefill_size_sampled_rows_and_linearity(ctx, bits, rows):
     """The benchmark's prefill layer at full width (4096 -> 12288) in one launch, at every rate
