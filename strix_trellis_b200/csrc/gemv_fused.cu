@@ -580,6 +580,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_row_kernel(const GemvArgs ar
 #pragma unroll
         for (int j = 0; j < 4; ++j) su[j] = c.w.suh[(size_t)my_hb * 128 + lane + 32 * j];
     }
+    // The activation row may still be in flight from the prior grid, or cold in DRAM when it came
+    // from the host: ask the L2 for this CTA's part of it now, read it after the wait.
+    {
+        const int x_bytes = c.x_dtype == DT_F32 ? 4 : 2;
+        if (lane * 128 < 128 * x_bytes)
+            for (int item = warp; item < need; item += kConsumers) {
+                int hb = hb_first + item;
+                if (hb >= hblocks) hb -= hblocks;
+                prefetch_line_l2(reinterpret_cast<const unsigned char*>(c.x) + (size_t)hb * 128 * x_bytes + lane * 128);
+            }
+    }
     pdl_wait_prior_grid();  // x, y and the scratch may belong to the prior grid
     float xv[4] = {0.f, 0.f, 0.f, 0.f};
     if (warp < need) {

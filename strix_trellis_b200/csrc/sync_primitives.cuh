@@ -94,6 +94,12 @@ __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, ui
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
+// Asks the L2 for the 128-byte line that holds `p`.  The L2 is the point of coherence of the
+// device, so a line fetched early and written by another SM afterwards is still read correctly
+// from the L2 later.
+__device__ __forceinline__ void prefetch_line_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory");
+}
 // Programmatic dependent launch: let the next grid of the stream start its
 // independent prologue, and wait for the previous grid's memory before touching
 // anything it may have written.  Both are no-ops for an ordinary launch.
