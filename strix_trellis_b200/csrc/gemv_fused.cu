@@ -535,6 +535,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_row_kernel(const GemvArgs ar
 
     if (warp == kConsumers + 1) {
         // ---- epilogue warp: output stages of the blocks that need nobody else ---------------
+        // Output scales and bias of every column block this CTA touches are weights, cold in DRAM,
+        // and are needed at the very end of a block: ask the L2 for them now.
+        for (int nb = mine.begin / hblocks, last = (mine.end - 1) / hblocks; nb <= last && my_units > 0; ++nb) {
+            if (lane < 2) prefetch_line_l2(c.w.svh + (size_t)nb * 128 + lane * 64);
+            else if (lane < 6 && c.w.bias) prefetch_line_l2(c.w.bias + (size_t)nb * 128 + (lane - 2) * 32);
+        }
         pdl_wait_prior_grid();  // y may belong to the prior grid
         int done = 0, flush = 0;
         while (done < my_units) {
